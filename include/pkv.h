@@ -1,0 +1,260 @@
+/*
+ * pkv.h -- C ABI of the B200 (sm_100a) paged-KV hot path for llm-engine.
+ *
+ * This is the whole drop-in boundary: plain pointers and sizes, no C++ or
+ * framework types.  Every entry point returns a status code (0 = PKV_OK,
+ * negative = error, see pkv_status_string / pkv_last_error), never throws,
+ * never synchronises the device, never allocates device memory, and enqueues
+ * its work on the CUDA stream it is given (NULL = the legacy default stream,
+ * which is what llm-engine passes at every call site,
+ * src/model/cuda/cuda_model.cu:347-390).  All data pointers are DEVICE pointers
+ * unless a parameter is named h_* or documented as host memory.
+ *
+ * Each declaration names the llm-engine interface it replaces (file:line within
+ * that project).  Layout conventions are llm-engine's own:
+ *   - K and V pools are separate arrays [num_blocks*block_size slots][kv_heads][head_dim],
+ *     row-major (src/model/cuda/cuda_model.cu:276-285, src/model/cpu/cpu_model.cpp:83-87);
+ *   - slot(pos) = block_table[pos / block_size] * block_size + pos % block_size
+ *     (include/engine/kv_cache.h:29-31);
+ *   - q / out rows are [n_tokens][q_heads][head_dim]; query head h reads kv head
+ *     h / (q_heads / kv_heads) (include/engine/ops.h:79-86);
+ *   - block_tables is the step's concatenation of every distinct sequence's
+ *     table, table_offset[s] its start, token_seq[t] the step-local sequence of
+ *     packed token t, token_pos[t] its absolute position; a token attends
+ *     positions 0..token_pos[t] inclusive (include/engine/cuda_kernels.h:44-53).
+ */
+#ifndef PKV_H_
+#define PKV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PKV_ABI_VERSION 1
+
+typedef void* pkv_stream; /* a cudaStream_t */
+
+enum pkv_status {
+  PKV_OK = 0,
+  PKV_E_ARG = -1,         /* null pointer, negative size, misaligned pointer */
+  PKV_E_UNSUPPORTED = -2, /* geometry outside what the kernels implement */
+  PKV_E_WORKSPACE = -3,   /* workspace missing or too small for the request */
+  PKV_E_CUDA = -4,        /* the CUDA runtime refused the launch or a copy */
+  PKV_E_NOMEM = -5,       /* block pool exhausted (host bookkeeping) */
+  PKV_E_STATE = -6        /* handle used in a way its state does not allow */
+};
+
+int pkv_abi_version(void);
+/* Static description of a status code. */
+const char* pkv_status_string(int status);
+/* Detail of the calling thread's most recent failure ("" if none). */
+const char* pkv_last_error(void);
+
+/* ------------------------------------------------------------------ a1 ----
+ * K/V append.  Replaces engine::launch_store_kv (include/engine/cuda_kernels.h:43-45,
+ * src/kernels/store_kv.cu:20-36) and the CPU memcpy pair
+ * (src/model/cpu/cpu_model.cpp:153-157):
+ *     k_cache[slots[t]][:] = k[t][:],  v_cache[slots[t]][:] = v[t][:]   for t < n_tokens.
+ * Bit-exact byte copy; duplicate slots are allowed only with identical payloads
+ * (llm-engine re-writes a shared full block with the same values,
+ * src/scheduler/scheduler.cpp:60).  n_tokens <= 0 or kv_dim <= 0 is a no-op
+ * returning PKV_OK, as in the reference launcher. */
+int pkv_append_f16(const void* k, const void* v, const int* slots, void* k_cache, void* v_cache,
+                   int n_tokens, int kv_dim, pkv_stream stream);
+int pkv_append_bf16(const void* k, const void* v, const int* slots, void* k_cache, void* v_cache,
+                    int n_tokens, int kv_dim, pkv_stream stream);
+int pkv_append_f32(const void* k, const void* v, const int* slots, void* k_cache, void* v_cache,
+                   int n_tokens, int kv_dim, pkv_stream stream);
+
+/* ------------------------------------------------------------------ a2 ----
+ * Paged decode attention.  Replaces engine::launch_attention_decode and
+ * engine::launch_attention_decode_gqa (include/engine/cuda_kernels.h:48-62,
+ * src/kernels/attention_decode.cu:133-161, src/kernels/attention_decode_gqa.cu:200-232);
+ * the arithmetic it must agree with is ref::paged_attention_head
+ * (include/engine/ops.h:87-111).  Arguments up to `stream` are the reference
+ * launcher's; `workspace` is caller-owned scratch for split-K over long contexts:
+ *   - workspace == NULL: every (token, kv head) is handled by one thread block
+ *     over its whole history (correct for any length, slow for long ones);
+ *   - otherwise at least pkv_decode_workspace_bytes(...) bytes, 256-byte aligned.
+ *     It carries no state between calls of this all-in-one form.
+ * n_tokens <= 0 is a no-op.  Geometry limits: q_heads % kv_heads == 0,
+ * head_dim <= 256, block_size >= 1. */
+size_t pkv_decode_workspace_bytes(int n_tokens, int q_heads, int kv_heads, int head_dim);
+
+int pkv_decode_attn_f16(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                        const int* table_offset, const int* token_seq, const int* token_pos, void* out,
+                        int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size,
+                        float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+int pkv_decode_attn_bf16(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                         const int* table_offset, const int* token_seq, const int* token_pos, void* out,
+                         int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size,
+                         float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+int pkv_decode_attn_f32(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                        const int* table_offset, const int* token_seq, const int* token_pos, void* out,
+                        int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size,
+                        float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+
+/* Plan-once form.  A decode step calls attention once per layer with the SAME
+ * index arrays (src/model/cuda/cuda_model.cu:349-377), so the split-K work list
+ * can be built once per step and reused by every layer.
+ *
+ * pkv_decode_plan_host builds the list on the host from the host copy of
+ * token_pos that the caller already has before uploading it
+ * (src/model/cuda/cuda_model.cu:434-447,479), writes its image to `h_staging`
+ * (host memory, pinned for a truly asynchronous copy; at least
+ * pkv_decode_plan_staging_bytes(n_tokens, kv_heads) bytes; must stay untouched
+ * until the copy has run) and enqueues one host-to-device copy into `workspace`.
+ * pkv_decode_plan_device does the same from the device copy of token_pos with a
+ * single small kernel, for callers that hold no host copy.
+ * The plan is valid for any number of pkv_decode_attn_planned_* calls on the
+ * same stream with the same n_tokens / heads / head_dim / token_pos contents. */
+typedef struct pkv_decode_plan {
+  int n_tokens;
+  int q_heads, kv_heads, head_dim;
+  int chunk;      /* keys per work item; 0 = no splitting */
+  int n_items;    /* exact item count when host-built, upper bound when device-built */
+  int exact;      /* 1 if n_items is exact */
+  int reserved;
+} pkv_decode_plan;
+
+size_t pkv_decode_plan_staging_bytes(int n_tokens, int kv_heads);
+int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                         void* h_staging, size_t staging_bytes, void* workspace, size_t workspace_bytes,
+                         pkv_stream stream, pkv_decode_plan* plan);
+int pkv_decode_plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                           void* workspace, size_t workspace_bytes, pkv_stream stream,
+                           pkv_decode_plan* plan);
+int pkv_decode_attn_planned_f16(const pkv_decode_plan* plan, const void* q, const void* k_cache,
+                                const void* v_cache, const int* block_tables, const int* table_offset,
+                                const int* token_seq, const int* token_pos, void* out, int block_size,
+                                float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+int pkv_decode_attn_planned_bf16(const pkv_decode_plan* plan, const void* q, const void* k_cache,
+                                 const void* v_cache, const int* block_tables, const int* table_offset,
+                                 const int* token_seq, const int* token_pos, void* out, int block_size,
+                                 float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+int pkv_decode_attn_planned_f32(const pkv_decode_plan* plan, const void* q, const void* k_cache,
+                                const void* v_cache, const int* block_tables, const int* table_offset,
+                                const int* token_seq, const int* token_pos, void* out, int block_size,
+                                float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+
+/* ------------------------------------------------------------------ a3 ----
+ * Paged (chunked) prefill attention on the tensor cores.  llm-engine has no such
+ * kernel (src/kernels/attention_prefill.cu:1 is a stub; prefill tokens go through
+ * the decode launcher, src/model/cuda/cuda_model.cu:370-377); the result it must
+ * agree with is still ref::paged_attention_head applied to every (token, head)
+ * of the chunk (include/engine/ops.h:87-111).
+ * Sequence s (step-local index, table at block_tables + table_offset[s]) brings
+ * q_len[s] new tokens, packed as rows q_start[s] .. q_start[s]+q_len[s]-1 of q/out,
+ * at absolute positions ctx_len[s] .. ctx_len[s]+q_len[s]-1; row i attends
+ * positions 0 .. ctx_len[s]+i (causal over cached plus new tokens).  K/V of the
+ * chunk must already be in the pool (pkv_append_* first, as the reference orders
+ * store_kv before attention, src/model/cuda/cuda_model.cu:362-368).
+ * max_q_len >= max_s q_len[s] sizes the grid (the caller's chunk size,
+ * include/engine/scheduler.h:26).  bf16 and f16, head_dim 64 or 128,
+ * block_size a power of two in 8..128, q_heads % kv_heads == 0. */
+int pkv_prefill_attn_bf16(const void* q, const void* k_cache, const void* v_cache,
+                          const int* block_tables, const int* table_offset, const int* q_start,
+                          const int* q_len, const int* ctx_len, void* out, int n_seqs, int max_q_len,
+                          int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks,
+                          float scale, pkv_stream stream);
+int pkv_prefill_attn_f16(const void* q, const void* k_cache, const void* v_cache,
+                         const int* block_tables, const int* table_offset, const int* q_start,
+                         const int* q_len, const int* ctx_len, void* out, int n_seqs, int max_q_len,
+                         int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks,
+                         float scale, pkv_stream stream);
+
+/* ------------------------------------------------------------------ a5 ----
+ * Prefix-cache copy-on-write block copy.  No llm-engine counterpart (it shares
+ * full blocks only and therefore never copies, docs/design.md:36); semantics are
+ * memcpy's: for each pair i, block src_dst_pairs[2i] is copied over block
+ * src_dst_pairs[2i+1] in both pools.  Destinations must be distinct from each
+ * other and from every source of the same call.  Bit-exact.
+ * pkv_copy_blocks_layers does the same for n_caches pools at once (every layer's
+ * K and V): d_cache_ptrs is a device array of n_caches pool base pointers. */
+int pkv_copy_blocks_f16(void* k_cache, void* v_cache, const int* src_dst_pairs, int n_pairs,
+                        int block_size, int kv_dim, pkv_stream stream);
+int pkv_copy_blocks_bf16(void* k_cache, void* v_cache, const int* src_dst_pairs, int n_pairs,
+                         int block_size, int kv_dim, pkv_stream stream);
+int pkv_copy_blocks_f32(void* k_cache, void* v_cache, const int* src_dst_pairs, int n_pairs,
+                        int block_size, int kv_dim, pkv_stream stream);
+int pkv_copy_blocks_layers(void* const* d_cache_ptrs, int n_caches, const int* src_dst_pairs,
+                           int n_pairs, size_t block_bytes, pkv_stream stream);
+
+/* ------------------------------------------------------------------ a4 ----
+ * Step-index packing (host).  Replaces the loop of CudaModel::upload_step_indices
+ * (src/model/cuda/cuda_model.cu:453-473): sequences are numbered in order of
+ * first appearance among the packed tokens, each distinct sequence's block table
+ * is appended once to `tables`, and slots[i] = slot(tok_pos[i]).  All pointers
+ * are HOST pointers.  tok_seq_key[i] identifies token i's sequence (the reference
+ * compares Sequence pointers); tok_blocks[i] / tok_num_blocks[i] is that
+ * sequence's block table.  Outputs: slots[n_tokens], token_seq[n_tokens],
+ * tables[tables_cap], table_offset[offsets_cap]; *n_seqs and *n_table receive the
+ * counts.  PKV_E_WORKSPACE if a capacity is too small; PKV_E_ARG if a position
+ * lies beyond its table. */
+int pkv_step_pack(int n_tokens, const uint64_t* tok_seq_key, const int32_t* const* tok_blocks,
+                  const int* tok_num_blocks, const int* tok_pos, int block_size, int* slots,
+                  int* token_seq, int* tables, size_t tables_cap, int* table_offset,
+                  size_t offsets_cap, int* n_seqs, int* n_table);
+
+/* ------------------------------------------------------------------ a0 ----
+ * KV block bookkeeping (host).  C handles over the C++ KVCacheManager / BlockTable
+ * of include/pkv_kv_cache.hpp, which keep the public surface of llm-engine's
+ * classes (include/engine/kv_cache.h:21-99, src/kv_cache/block_allocator.cpp:8-142)
+ * and hand out identical block ids, hashes and statistics. */
+typedef struct pkv_kvmgr pkv_kvmgr;
+typedef struct pkv_table pkv_table;
+
+pkv_kvmgr* pkv_kvmgr_create(int num_blocks, int block_size, int enable_prefix_caching); /* NULL on bad args */
+void pkv_kvmgr_destroy(pkv_kvmgr* m);
+pkv_table* pkv_table_create(void);
+void pkv_table_destroy(pkv_table* t);
+
+/* kv_cache.h:62 -- cached token count, or -1 when the pool cannot fit the prompt. */
+int pkv_kvmgr_allocate_prompt(pkv_kvmgr* m, pkv_table* t, const int32_t* tokens, int n_tokens);
+/* kv_cache.h:66 -- 1 on success, 0 when out of blocks. */
+int pkv_kvmgr_ensure_slot(pkv_kvmgr* m, pkv_table* t, int num_tokens);
+/* kv_cache.h:72 */
+void pkv_kvmgr_commit_computed(pkv_kvmgr* m, pkv_table* t, const int32_t* tokens, int n_tokens, int num_computed);
+/* kv_cache.h:76 */
+void pkv_kvmgr_free(pkv_kvmgr* m, pkv_table* t);
+/* kv_cache.h:79 */
+int pkv_kvmgr_lookup_cached_prefix(const pkv_kvmgr* m, const int32_t* tokens, int n_tokens);
+/* kv_cache.h:81, block_allocator.cpp:16-23 */
+uint64_t pkv_hash_block(uint64_t prev_hash, const int32_t* tokens, int n);
+/* kv_cache.h:46-55 */
+int pkv_kvmgr_block_size(const pkv_kvmgr* m);
+int pkv_kvmgr_num_total_blocks(const pkv_kvmgr* m);
+int pkv_kvmgr_capacity_tokens(const pkv_kvmgr* m);
+int pkv_kvmgr_num_free_blocks(const pkv_kvmgr* m);
+int pkv_kvmgr_num_cached_blocks(const pkv_kvmgr* m);
+int pkv_kvmgr_num_available_blocks(const pkv_kvmgr* m);
+int pkv_kvmgr_num_used_blocks(const pkv_kvmgr* m);
+/* kv_cache.h:34-40 -- out[5] = prefix_queries, prefix_hit_blocks, prefix_total_blocks,
+ * evictions, allocation_failures */
+void pkv_kvmgr_stats(const pkv_kvmgr* m, uint64_t out[5]);
+int pkv_kvmgr_ref_count(const pkv_kvmgr* m, int block);
+
+/* kv_cache.h:21-32 */
+int pkv_table_num_blocks(const pkv_table* t);
+int pkv_table_num_committed(const pkv_table* t);
+const int32_t* pkv_table_blocks(const pkv_table* t);  /* valid until the table is next modified */
+const uint64_t* pkv_table_hashes(const pkv_table* t);
+int64_t pkv_table_slot(const pkv_table* t, int pos, int block_size);
+
+/* Copy-on-write bookkeeping; additive, no llm-engine counterpart.
+ * fork: `child` (empty) comes to share every block of `parent`, the partial last
+ * block included (reference counts +1).
+ * cow: call before writing position `write_pos` of `t`.  If that block is still
+ * shared and not yet committed, `t` moves to a private block: returns 1 with
+ * *src / *dst for pkv_copy_blocks_*, 0 when no copy is needed, PKV_E_NOMEM when
+ * the pool is exhausted. */
+int pkv_kvmgr_fork(pkv_kvmgr* m, const pkv_table* parent, pkv_table* child);
+int pkv_kvmgr_cow(pkv_kvmgr* m, pkv_table* t, int write_pos, int* src, int* dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PKV_H_ */

@@ -1,0 +1,463 @@
+// C-ABI entry points for paged decode attention (include/pkv.h, section a2):
+// argument validation, split-K planning (host and device), kernel selection.
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "decode_attn.cuh"
+#include "launch_util.hpp"
+#include "status.hpp"
+
+namespace pkv {
+namespace {
+
+// ---- tuning knobs (read once) ---------------------------------------------------
+struct Tuning {
+  int target_ctas;   // thread blocks the planner aims for when it splits
+  int wave_ctas;     // below this many blocks, smaller chunks are tried
+  int forced_chunk;  // 0 = rule
+  int variant;       // ring depth / occupancy variant of the tensor-core kernel
+  int max_extra_cap;
+};
+int env_int(const char* name, int dflt) {
+  const char* e = std::getenv(name);
+  if (!e || !*e) return dflt;
+  return std::atoi(e);
+}
+const Tuning& tuning() {
+  static const Tuning t = [] {
+    Tuning x;
+    x.target_ctas = env_int("PKV_DECODE_TARGET_CTAS", 4736);
+    x.wave_ctas = env_int("PKV_DECODE_WAVE_CTAS", 592);
+    x.forced_chunk = env_int("PKV_DECODE_CHUNK", 0);
+    x.variant = env_int("PKV_DECODE_VARIANT", 0);
+    x.max_extra_cap = 16384;
+    return x;
+  }();
+  return t;
+}
+
+int max_extra(int kv_heads) { return (tuning().max_extra_cap + kv_heads - 1) / kv_heads; }
+
+// ---- device planner ---------------------------------------------------------------
+// One block builds the whole work list from the device copy of token_pos.
+constexpr int kPlanThreads = 1024;
+
+__global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int* __restrict__ token_pos, int n_tokens,
+                                                                    int kv_heads, long long extra_budget,
+                                                                    int wave_ctas, int forced_chunk,
+                                                                    PlanHeader* header, TokSplit* tok_split,
+                                                                    int* counters, WorkItem* items) {
+  __shared__ unsigned long long sm_items[kNumChunkCandidates];
+  __shared__ int sm_chunk;
+  __shared__ int sm_scan_items[kPlanThreads / 32], sm_scan_parts[kPlanThreads / 32];
+  __shared__ int sm_carry_items, sm_carry_parts;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < kNumChunkCandidates) sm_items[tid] = 0ull;
+  if (tid == 0) { sm_carry_items = 0; sm_carry_parts = 0; }
+  __syncthreads();
+  {
+    unsigned long long loc[kNumChunkCandidates];
+#pragma unroll
+    for (int j = 0; j < kNumChunkCandidates; ++j) loc[j] = 0ull;
+    for (int t = tid; t < n_tokens; t += kPlanThreads) {
+      const int L = max(token_pos[t], 0) + 1;
+#pragma unroll
+      for (int j = 0; j < kNumChunkCandidates; ++j) loc[j] += static_cast<unsigned>((L + (kMinChunk << j) - 1) / (kMinChunk << j));
+    }
+#pragma unroll
+    for (int j = 0; j < kNumChunkCandidates; ++j) {
+      unsigned long long v = loc[j];
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && v) atomicAdd(&sm_items[j], v);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    long long items_at[kNumChunkCandidates];
+    for (int j = 0; j < kNumChunkCandidates; ++j) items_at[j] = static_cast<long long>(sm_items[j]);
+    sm_chunk = choose_chunk(items_at, n_tokens, kv_heads, extra_budget, wave_ctas, forced_chunk);
+  }
+  __syncthreads();
+  const int chunk = sm_chunk;
+
+  for (int base = 0; base < n_tokens; base += kPlanThreads) {
+    const int t = base + tid;
+    int L = 0, ns = 0;
+    if (t < n_tokens) {
+      L = max(token_pos[t], 0) + 1;
+      ns = chunk > 0 ? (L + chunk - 1) / chunk : 1;
+    }
+    const int np = ns > 1 ? ns : 0;
+    // inclusive scans of ns and np across the block
+    int si = ns, sp = np;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, si, o), b = __shfl_up_sync(0xffffffffu, sp, o);
+      if (lane >= o) { si += a; sp += b; }
+    }
+    if (lane == 31) { sm_scan_items[warp] = si; sm_scan_parts[warp] = sp; }
+    __syncthreads();
+    if (warp == 0) {
+      int a = sm_scan_items[lane], b = sm_scan_parts[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(0xffffffffu, a, o), y = __shfl_up_sync(0xffffffffu, b, o);
+        if (lane >= o) { a += x; b += y; }
+      }
+      sm_scan_items[lane] = a;
+      sm_scan_parts[lane] = b;
+    }
+    __syncthreads();
+    const int item0 = sm_carry_items + (warp ? sm_scan_items[warp - 1] : 0) + si - ns;
+    const int part0 = sm_carry_parts + (warp ? sm_scan_parts[warp - 1] : 0) + sp - np;
+    if (t < n_tokens) {
+      tok_split[t] = TokSplit{part0, ns};
+      for (int s = 0; s < ns; ++s) {
+        const int b = chunk > 0 ? s * chunk : 0;
+        const int len = chunk > 0 ? min(chunk, L - b) : L;
+        items[item0 + s] = WorkItem{t, b, len, ns > 1 ? part0 + s : -1};
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      sm_carry_items += sm_scan_items[kPlanThreads / 32 - 1];
+      sm_carry_parts += sm_scan_parts[kPlanThreads / 32 - 1];
+    }
+    __syncthreads();
+  }
+  for (int i = tid; i < n_tokens * kv_heads; i += kPlanThreads) counters[i] = 0;
+  if (tid == 0) {
+    header->magic = kPlanMagic;
+    header->n_items = sm_carry_items;
+    header->chunk = chunk;
+    header->n_tokens = n_tokens;
+    header->n_parts = sm_carry_parts;
+    header->kv_heads = kv_heads;
+    header->pad[0] = header->pad[1] = 0;
+  }
+}
+
+// ---- kernel launch ----------------------------------------------------------------
+template <typename T> struct IsF32 { static constexpr bool value = false; };
+template <> struct IsF32<float> { static constexpr bool value = true; };
+
+template <typename T, int D, int STAGES, int MINB>
+int launch_mma(const DecodeArgs& a, int grid, cudaStream_t stream) {
+  using S = MmaSmem<D, STAGES>;
+  auto kern = decode_mma_kernel<T, D, STAGES, MINB>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve %d bytes of shared memory: %s", S::kBytes, cudaGetErrorString(e));
+    configured_device = dev;
+  }
+  kern<<<grid, kDecodeThreads, S::kBytes, stream>>>(a);
+  return check_launch("decode_mma_kernel");
+}
+
+template <typename T, int DJ>
+int launch_simt(const DecodeArgs& a, int grid, cudaStream_t stream) {
+  const size_t smem = simt_smem_bytes(a.head_dim);
+  auto kern = decode_simt_kernel<T, DJ>;
+  if (smem > 48 * 1024) {
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve shared memory: %s", cudaGetErrorString(e));
+      configured_device = dev;
+    }
+  }
+  kern<<<grid, kDecodeThreads, smem, stream>>>(a);
+  return check_launch("decode_simt_kernel");
+}
+
+template <typename T>
+int launch_decode(const DecodeArgs& a, int grid, cudaStream_t stream) {
+  if constexpr (!IsF32<T>::value) {
+    const bool mma_ok = (a.head_dim == 64 || a.head_dim == 128) && a.group <= 16 && a.bs_log2 >= 0;
+    if (mma_ok) {
+      const int variant = tuning().variant;
+      if (a.head_dim == 64) {
+        if (variant == 1) return launch_mma<T, 64, 3, 4>(a, grid, stream);
+        if (variant == 2) return launch_mma<T, 64, 6, 2>(a, grid, stream);
+        return launch_mma<T, 64, 4, 3>(a, grid, stream);
+      }
+      return launch_mma<T, 128, 3, 2>(a, grid, stream);
+    }
+  }
+  const int dj = (a.head_dim + 31) / 32;
+  if (dj <= 2) return launch_simt<T, 2>(a, grid, stream);
+  if (dj <= 4) return launch_simt<T, 4>(a, grid, stream);
+  return launch_simt<T, 8>(a, grid, stream);
+}
+
+int validate_geometry(const char* fn, int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size) {
+  if (q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || block_size <= 0)
+    return fail(PKV_E_ARG, "%s: q_heads %d, kv_heads %d, head_dim %d, block_size %d must all be > 0", fn, q_heads, kv_heads, head_dim, block_size);
+  if (q_heads % kv_heads != 0)
+    return fail(PKV_E_UNSUPPORTED, "%s: q_heads %d is not a multiple of kv_heads %d", fn, q_heads, kv_heads);
+  if (head_dim > 256)
+    return fail(PKV_E_UNSUPPORTED, "%s: head_dim %d exceeds 256, the largest the accumulators cover", fn, head_dim);
+  (void)n_tokens;
+  return PKV_OK;
+}
+
+int validate_pointers(const char* fn, const void* q, const void* kc, const void* vc, const int* bt, const int* to,
+                      const int* ts, const int* tp, const void* out, size_t row_bytes) {
+  if (!q || !kc || !vc || !bt || !to || !ts || !tp || !out) return fail(PKV_E_ARG, "%s: null device pointer", fn);
+  if (row_bytes % 16 == 0 &&
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
+        reinterpret_cast<uintptr_t>(out)) & 15))
+    return fail(PKV_E_ARG, "%s: q, out and the K/V pools must be 16-byte aligned", fn);
+  return PKV_OK;
+}
+
+int log2_exact(int x) {
+  if (x <= 0 || (x & (x - 1))) return -1;
+  int l = 0;
+  while ((1 << l) < x) ++l;
+  return l;
+}
+
+void fill_args(DecodeArgs& a, const void* q, const void* kc, const void* vc, const int* bt, const int* to,
+               const int* ts, const int* tp, void* out, int n_tokens, int q_heads, int kv_heads, int head_dim,
+               int block_size, float scale) {
+  a.q = q; a.k_cache = kc; a.v_cache = vc;
+  a.block_tables = bt; a.table_offset = to; a.token_seq = ts; a.token_pos = tp;
+  a.out = out;
+  a.n_tokens = n_tokens; a.q_heads = q_heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
+  a.group = q_heads / kv_heads;
+  a.block_size = block_size; a.bs_log2 = log2_exact(block_size);
+  a.scale = scale;
+  a.header = nullptr; a.items = nullptr; a.tok_split = nullptr; a.counters = nullptr;
+  a.part_ml = nullptr; a.part_acc = nullptr;
+  a.direct = 1;
+}
+
+void attach_workspace(DecodeArgs& a, void* workspace, const WsLayout& w) {
+  char* base = static_cast<char*>(workspace);
+  a.header = reinterpret_cast<const PlanHeader*>(base);
+  a.tok_split = reinterpret_cast<const TokSplit*>(base + w.off_tok);
+  a.counters = reinterpret_cast<int*>(base + w.off_cnt);
+  a.items = reinterpret_cast<const WorkItem*>(base + w.off_items);
+  a.part_ml = reinterpret_cast<float*>(base + w.off_ml);
+  a.part_acc = reinterpret_cast<float*>(base + w.off_acc);
+  a.direct = 0;
+}
+
+int persistent_grid() {
+  static thread_local int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms * 4;
+}
+
+// Budget of extra items for this workspace: what fits, capped by the target grid.
+int plan_budget(int n_tokens, int q_heads, int kv_heads, int head_dim, size_t workspace_bytes, WsLayout* w) {
+  const int fit = ws_extra_for_bytes(n_tokens, q_heads, kv_heads, head_dim, workspace_bytes, max_extra(kv_heads));
+  if (fit < 0) return -1;
+  *w = ws_layout(n_tokens, q_heads, kv_heads, head_dim, fit);
+  const int target_extra = (tuning().target_ctas + kv_heads - 1) / kv_heads;
+  return fit < target_extra ? fit : target_extra;
+}
+
+int plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim, void* workspace,
+                size_t workspace_bytes, cudaStream_t stream, pkv_decode_plan* plan) {
+  if (!token_pos || !workspace || !plan) return fail(PKV_E_ARG, "pkv_decode_plan_device: null pointer");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PKV_E_ARG, "pkv_decode_plan_device: workspace must be 256-byte aligned");
+  WsLayout w;
+  const int budget = plan_budget(n_tokens, q_heads, kv_heads, head_dim, workspace_bytes, &w);
+  if (budget < 0)
+    return fail(PKV_E_WORKSPACE, "pkv_decode_plan_device: workspace of %zu bytes cannot hold the plan for %d tokens", workspace_bytes, n_tokens);
+  char* base = static_cast<char*>(workspace);
+  decode_plan_kernel<<<1, kPlanThreads, 0, stream>>>(
+      token_pos, n_tokens, kv_heads, budget, tuning().wave_ctas, tuning().forced_chunk,
+      reinterpret_cast<PlanHeader*>(base), reinterpret_cast<TokSplit*>(base + w.off_tok),
+      reinterpret_cast<int*>(base + w.off_cnt), reinterpret_cast<WorkItem*>(base + w.off_items));
+  int st = check_launch("decode_plan_kernel");
+  if (st != PKV_OK) return st;
+  plan->n_tokens = n_tokens; plan->q_heads = q_heads; plan->kv_heads = kv_heads; plan->head_dim = head_dim;
+  plan->chunk = -1;                      // decided on the device
+  plan->n_items = n_tokens + budget;     // upper bound
+  plan->exact = 0;
+  plan->reserved = 0;
+  return PKV_OK;
+}
+
+template <typename T>
+int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, const void* vc, const int* bt,
+                   const int* to, const int* ts, const int* tp, void* out, int block_size, float scale,
+                   void* workspace, size_t workspace_bytes, pkv_stream stream) {
+  const char* fn = "pkv_decode_attn_planned";
+  if (!plan) return fail(PKV_E_ARG, "%s: null plan", fn);
+  if (plan->n_tokens <= 0) return PKV_OK;
+  int st = validate_geometry(fn, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size);
+  if (st != PKV_OK) return st;
+  st = validate_pointers(fn, q, kc, vc, bt, to, ts, tp, out, sizeof(T) * static_cast<size_t>(plan->head_dim));
+  if (st != PKV_OK) return st;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255)) return fail(PKV_E_ARG, "%s: workspace null or not 256-byte aligned", fn);
+  WsLayout w;
+  if (plan_budget(plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, workspace_bytes, &w) < 0)
+    return fail(PKV_E_WORKSPACE, "%s: workspace of %zu bytes is smaller than the plan it should hold", fn, workspace_bytes);
+  DecodeArgs a;
+  fill_args(a, q, kc, vc, bt, to, ts, tp, out, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size, scale);
+  attach_workspace(a, workspace, w);
+  long long blocks = static_cast<long long>(plan->n_items) * plan->kv_heads;
+  if (!plan->exact && blocks > persistent_grid()) blocks = persistent_grid();
+  if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
+  return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream));
+}
+
+template <typename T>
+int decode_all_in_one(const void* q, const void* kc, const void* vc, const int* bt, const int* to, const int* ts,
+                      const int* tp, void* out, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                      int block_size, float scale, void* workspace, size_t workspace_bytes, pkv_stream stream) {
+  const char* fn = "pkv_decode_attn";
+  if (n_tokens <= 0 || q_heads <= 0) return PKV_OK;  // the reference launchers' silent no-op
+  int st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, block_size);
+  if (st != PKV_OK) return st;
+  st = validate_pointers(fn, q, kc, vc, bt, to, ts, tp, out, sizeof(T) * static_cast<size_t>(head_dim));
+  if (st != PKV_OK) return st;
+  if (!workspace) {
+    DecodeArgs a;
+    fill_args(a, q, kc, vc, bt, to, ts, tp, out, n_tokens, q_heads, kv_heads, head_dim, block_size, scale);
+    long long blocks = static_cast<long long>(n_tokens) * kv_heads;
+    if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
+    return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream));
+  }
+  pkv_decode_plan plan;
+  st = plan_device(tp, n_tokens, q_heads, kv_heads, head_dim, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), &plan);
+  if (st != PKV_OK) return st;
+  return decode_planned<T>(&plan, q, kc, vc, bt, to, ts, tp, out, block_size, scale, workspace, workspace_bytes, stream);
+}
+
+}  // namespace
+}  // namespace pkv
+
+using namespace pkv;
+
+extern "C" {
+
+size_t pkv_decode_workspace_bytes(int n_tokens, int q_heads, int kv_heads, int head_dim) {
+  if (n_tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0) return 0;
+  return ws_layout(n_tokens, q_heads, kv_heads, head_dim, max_extra(kv_heads)).total;
+}
+
+size_t pkv_decode_plan_staging_bytes(int n_tokens, int kv_heads) {
+  if (n_tokens <= 0 || kv_heads <= 0) return 0;
+  const WsLayout w = ws_layout(n_tokens, 1, kv_heads, 1, max_extra(kv_heads));
+  return w.off_ml;  // header .. end of items
+}
+
+int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                         void* h_staging, size_t staging_bytes, void* workspace, size_t workspace_bytes,
+                         pkv_stream stream, pkv_decode_plan* plan) {
+  const char* fn = "pkv_decode_plan_host";
+  if (!plan) return fail(PKV_E_ARG, "%s: null plan", fn);
+  std::memset(plan, 0, sizeof(*plan));
+  if (n_tokens <= 0) return PKV_OK;
+  if (!h_token_pos || !h_staging || !workspace) return fail(PKV_E_ARG, "%s: null pointer", fn);
+  int st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, 1);
+  if (st != PKV_OK) return st;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PKV_E_ARG, "%s: workspace must be 256-byte aligned", fn);
+  WsLayout w;
+  const int budget = plan_budget(n_tokens, q_heads, kv_heads, head_dim, workspace_bytes, &w);
+  if (budget < 0) return fail(PKV_E_WORKSPACE, "%s: workspace of %zu bytes cannot hold the plan for %d tokens", fn, workspace_bytes, n_tokens);
+
+  long long items_at[kNumChunkCandidates] = {0};
+  for (int t = 0; t < n_tokens; ++t) {
+    if (h_token_pos[t] < 0) return fail(PKV_E_ARG, "%s: token %d has negative position %d", fn, t, h_token_pos[t]);
+    const int L = h_token_pos[t] + 1;
+    for (int j = 0; j < kNumChunkCandidates; ++j) items_at[j] += (L + (kMinChunk << j) - 1) / (kMinChunk << j);
+  }
+  const int chunk = choose_chunk(items_at, n_tokens, kv_heads, budget, tuning().wave_ctas, tuning().forced_chunk);
+  long long n_items = n_tokens;
+  if (chunk > 0) {
+    n_items = 0;
+    for (int t = 0; t < n_tokens; ++t) n_items += (h_token_pos[t] + chunk) / chunk;
+  }
+  const size_t image = w.off_items + sizeof(WorkItem) * static_cast<size_t>(n_items);
+  if (image > staging_bytes) return fail(PKV_E_WORKSPACE, "%s: staging buffer of %zu bytes is smaller than the %zu-byte plan image", fn, staging_bytes, image);
+
+  char* img = static_cast<char*>(h_staging);
+  std::memset(img, 0, w.off_items);
+  PlanHeader* hd = reinterpret_cast<PlanHeader*>(img);
+  TokSplit* tsp = reinterpret_cast<TokSplit*>(img + w.off_tok);
+  WorkItem* it = reinterpret_cast<WorkItem*>(img + w.off_items);
+  int ni = 0, np = 0;
+  // Full-size chunks first, ragged tails afterwards: thread blocks are handed out
+  // in index order, so the short items end up filling the last wave.
+  for (int pass = 0; pass < 2; ++pass) {
+    for (int t = 0; t < n_tokens; ++t) {
+      const int L = h_token_pos[t] + 1;
+      const int ns = chunk > 0 ? (L + chunk - 1) / chunk : 1;
+      if (pass == 0) {
+        tsp[t] = TokSplit{np, ns};
+        if (ns > 1) np += ns;
+      }
+      for (int s = 0; s < ns; ++s) {
+        const int b = chunk > 0 ? s * chunk : 0;
+        const int len = chunk > 0 ? (L - b < chunk ? L - b : chunk) : L;
+        const bool full = chunk > 0 && len == chunk;
+        if (full != (pass == 0)) continue;
+        it[ni++] = WorkItem{t, b, len, ns > 1 ? tsp[t].part_base + s : -1};
+      }
+    }
+  }
+  hd->magic = kPlanMagic;
+  hd->n_items = ni;
+  hd->chunk = chunk;
+  hd->n_tokens = n_tokens;
+  hd->n_parts = np;
+  hd->kv_heads = kv_heads;
+  cudaError_t e = cudaMemcpyAsync(workspace, img, image, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: plan upload failed: %s", fn, cudaGetErrorString(e));
+  plan->n_tokens = n_tokens; plan->q_heads = q_heads; plan->kv_heads = kv_heads; plan->head_dim = head_dim;
+  plan->chunk = chunk;
+  plan->n_items = ni;
+  plan->exact = 1;
+  return PKV_OK;
+}
+
+int pkv_decode_plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                           void* workspace, size_t workspace_bytes, pkv_stream stream, pkv_decode_plan* plan) {
+  if (!plan) return fail(PKV_E_ARG, "pkv_decode_plan_device: null plan");
+  std::memset(plan, 0, sizeof(*plan));
+  if (n_tokens <= 0) return PKV_OK;
+  int st = validate_geometry("pkv_decode_plan_device", n_tokens, q_heads, kv_heads, head_dim, 1);
+  if (st != PKV_OK) return st;
+  return plan_device(token_pos, n_tokens, q_heads, kv_heads, head_dim, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), plan);
+}
+
+#define PKV_DECODE_ENTRY(SUFFIX, TYPE)                                                                               \
+  int pkv_decode_attn_##SUFFIX(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,     \
+                               const int* table_offset, const int* token_seq, const int* token_pos, void* out,      \
+                               int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size, float scale,  \
+                               void* workspace, size_t workspace_bytes, pkv_stream stream) {                        \
+    return decode_all_in_one<TYPE>(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,      \
+                                   n_tokens, q_heads, kv_heads, head_dim, block_size, scale, workspace,             \
+                                   workspace_bytes, stream);                                                        \
+  }                                                                                                                  \
+  int pkv_decode_attn_planned_##SUFFIX(const pkv_decode_plan* plan, const void* q, const void* k_cache,             \
+                                       const void* v_cache, const int* block_tables, const int* table_offset,       \
+                                       const int* token_seq, const int* token_pos, void* out, int block_size,       \
+                                       float scale, void* workspace, size_t workspace_bytes, pkv_stream stream) {   \
+    return decode_planned<TYPE>(plan, q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,   \
+                                block_size, scale, workspace, workspace_bytes, stream);                             \
+  }
+
+PKV_DECODE_ENTRY(f16, __half)
+PKV_DECODE_ENTRY(bf16, __nv_bfloat16)
+PKV_DECODE_ENTRY(f32, float)
+
+}  // extern "C"

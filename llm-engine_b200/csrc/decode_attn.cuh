@@ -1,0 +1,479 @@
+// Paged decode attention kernels (sm_100a).
+//
+// What they compute is ref::paged_attention_head of llm-engine
+// (include/engine/ops.h:87-111) for every packed token and query head: scores of
+// the query against keys 0..token_pos inclusive gathered through the sequence's
+// block table, softmax, weighted sum of the values.  How they compute it:
+//
+//   * one thread block per work item (token, key range) x kv head; ALL query
+//     heads of the GQA group share each K/V row read (the reference's baseline
+//     kernel reads it once per query head, src/kernels/attention_decode.cu:45-131);
+//   * 16-bit K/V: each warp streams 16-key tiles of its own through a private
+//     cp.async ring in shared memory (16-byte coalesced copies, XOR-swizzled rows,
+//     no block-wide barrier in the loop), feeds them to mma.sync m16n8k16 with the
+//     group's query heads as the M dimension, and keeps an online softmax in
+//     registers (quad shuffles for the row maximum);
+//   * fp32 K/V, or any geometry the tensor-core path does not cover: a SIMT kernel
+//     with the same work decomposition and fp32 arithmetic throughout;
+//   * split-K: partial (max, denominator, accumulator) per item in the caller's
+//     workspace, merged by whichever thread block finishes a token's last item
+//     (an arrival counter per (token, kv head); nothing ever waits on a flag).
+#pragma once
+
+#include "common.cuh"
+#include "decode_plan.hpp"
+
+namespace pkv {
+
+struct DecodeArgs {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int* block_tables;
+  const int* table_offset;
+  const int* token_seq;
+  const int* token_pos;
+  void* out;
+  int n_tokens, q_heads, kv_heads, head_dim, group;
+  int block_size, bs_log2;  // bs_log2 < 0 when block_size is not a power of two
+  float scale;
+  // plan (all null / 0 in direct mode)
+  const PlanHeader* header;
+  const WorkItem* items;
+  const TokSplit* tok_split;
+  int* counters;
+  float* part_ml;
+  float* part_acc;
+  int direct;  // 1: item i is token i over its whole history, no workspace
+};
+
+constexpr int kDecodeThreads = 128;
+constexpr int kDecodeWarps = 4;
+constexpr int kTileKeys = 16;
+
+__device__ __forceinline__ int64_t slot_of(const int* tbl, int pos, int block_size, int bs_log2) {
+  if (bs_log2 >= 0) return (static_cast<int64_t>(__ldg(tbl + (pos >> bs_log2))) << bs_log2) + (pos & (block_size - 1));
+  return static_cast<int64_t>(__ldg(tbl + pos / block_size)) * block_size + pos % block_size;
+}
+
+// exp in the domain the kernel's running maximum lives in: base 2 for the
+// tensor-core path (scores are pre-multiplied by log2 e), natural for fp32.
+template <bool LOG2> __device__ __forceinline__ float softmax_exp(float x) {
+  if (LOG2) return exp2f(x);
+  return expf(x);
+}
+
+// Merges the per-warp partial results of `rows` query heads (first one is
+// head0 of the token) held in shared memory and stores either the final output
+// rows or this item's split-K partial.
+//   sm_m, sm_l : [kDecodeWarps][16]      running max / denominator per warp and row
+//   sm_o       : [kDecodeWarps][16][ldo] unnormalised accumulators
+// Must be called by the whole block after a __syncthreads(); ends with one.
+template <typename T, bool LOG2>
+__device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int token, int head0, int rows, int part,
+                                                      const float* sm_m, const float* sm_l, const float* sm_o,
+                                                      int ldo, float* sm_w /*[kDecodeWarps+2][16]*/) {
+  const int D = a.head_dim;
+  const int tid = threadIdx.x;
+  if (tid < rows) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) m = fmaxf(m, sm_m[w * 16 + tid]);
+    float l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float mw = sm_m[w * 16 + tid];
+      const float f = (mw == -INFINITY) ? 0.f : softmax_exp<LOG2>(mw - m);
+      sm_w[w * 16 + tid] = f;
+      l += f * sm_l[w * 16 + tid];
+    }
+    sm_w[kDecodeWarps * 16 + tid] = m;
+    sm_w[(kDecodeWarps + 1) * 16 + tid] = l;
+  }
+  __syncthreads();
+  T* out = static_cast<T*>(a.out);
+  for (int idx = tid; idx < rows * D; idx += kDecodeThreads) {
+    const int r = idx / D, d = idx - r * D;
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) acc += sm_w[w * 16 + r] * sm_o[(w * 16 + r) * ldo + d];
+    const int head = head0 + r;
+    if (part < 0) {
+      const float l = sm_w[(kDecodeWarps + 1) * 16 + r];
+      out[(static_cast<size_t>(token) * a.q_heads + head) * D + d] = Elem<T>::from_f32(acc / l);
+    } else {
+      a.part_acc[(static_cast<size_t>(part) * a.q_heads + head) * D + d] = acc;
+    }
+  }
+  if (part >= 0 && tid < rows) {
+    float* ml = a.part_ml + (static_cast<size_t>(part) * a.q_heads + head0 + tid) * 2;
+    ml[0] = sm_w[kDecodeWarps * 16 + tid];
+    ml[1] = sm_w[(kDecodeWarps + 1) * 16 + tid];
+  }
+  __syncthreads();
+}
+
+// Split-K arrival: after this block's partial for (token, kvh) is written, count
+// it; the block that completes the count merges all partials of the group's
+// heads into the output and resets the counter for the next launch that reuses
+// the plan.  No block ever waits for another.
+template <typename T, bool LOG2>
+__device__ __forceinline__ void arrive_and_combine(const DecodeArgs& a, int token, int kvh, int* sm_flag) {
+  const TokSplit ts = a.tok_split[token];
+  __threadfence();  // partial stores visible device-wide before the ticket is taken
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(a.counters + token * a.kv_heads + kvh, 1);
+    *sm_flag = (ticket == ts.nsplits - 1);
+  }
+  __syncthreads();
+  if (!*sm_flag) return;
+  __threadfence();
+  const int D = a.head_dim;
+  T* out = static_cast<T*>(a.out);
+  const int head0 = kvh * a.group;
+  for (int idx = threadIdx.x; idx < a.group * D; idx += kDecodeThreads) {
+    const int r = idx / D, d = idx - r * D;
+    const int head = head0 + r;
+    float m = -INFINITY;
+    for (int s = 0; s < ts.nsplits; ++s)
+      m = fmaxf(m, __ldcg(a.part_ml + (static_cast<size_t>(ts.part_base + s) * a.q_heads + head) * 2));
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < ts.nsplits; ++s) {
+      const size_t p = static_cast<size_t>(ts.part_base + s) * a.q_heads + head;
+      const float f = softmax_exp<LOG2>(__ldcg(a.part_ml + p * 2) - m);
+      l += f * __ldcg(a.part_ml + p * 2 + 1);
+      acc += f * __ldcg(a.part_acc + p * D + d);
+    }
+    out[(static_cast<size_t>(token) * a.q_heads + head) * D + d] = Elem<T>::from_f32(acc / l);
+  }
+  if (threadIdx.x == 0) a.counters[token * a.kv_heads + kvh] = 0;
+}
+
+__device__ __forceinline__ void load_item(const DecodeArgs& a, int item, int& token, int& kv_begin, int& kv_len, int& part) {
+  if (a.direct) {
+    token = item;
+    kv_begin = 0;
+    kv_len = __ldg(a.token_pos + item) + 1;
+    part = -1;
+  } else {
+    const int4 it = __ldg(reinterpret_cast<const int4*>(a.items) + item);
+    token = it.x;
+    kv_begin = it.y;
+    kv_len = it.z;
+    part = it.w;
+  }
+}
+
+// ============================================================================
+// Tensor-core path: 16-bit K/V, head_dim D in {64, 128}, group <= 16,
+// block_size a power of two.
+// ============================================================================
+template <int D, int STAGES> struct MmaSmem {
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kTileBytes = kTileKeys * kRowBytes;            // one of K or V
+  static constexpr int kStageBytes = 2 * kTileBytes;                  // K then V
+  static constexpr int kWarpBytes = STAGES * kStageBytes;
+  static constexpr int kPipeBytes = kDecodeWarps * kWarpBytes;
+  static constexpr int kLdo = D + 4;
+  static constexpr int kMergeBytes = (kDecodeWarps * 16 * kLdo + 2 * kDecodeWarps * 16 + (kDecodeWarps + 2) * 16) * 4;
+  static constexpr int kBytes = (kPipeBytes > kMergeBytes ? kPipeBytes : kMergeBytes) + 16;
+};
+
+template <typename T, int D, int STAGES, int MIN_BLOCKS>
+__global__ void __launch_bounds__(kDecodeThreads, MIN_BLOCKS) decode_mma_kernel(const DecodeArgs a) {
+  using S = MmaSmem<D, STAGES>;
+  constexpr int KS = D / 16;             // k-steps of Q.K^T, and pairs of dim-tiles of P.V
+  constexpr int CH = D / 8;              // 16-byte chunks per K/V row
+  constexpr int ROWS_PER_PASS = 32 / CH; // rows one warp-wide cp.async covers
+  constexpr int PASSES = kTileKeys / ROWS_PER_PASS;
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int sm_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const uint32_t warp_smem = smem_u32(smem_raw) + warp * S::kWarpBytes;
+  const int kv_dim = a.kv_heads * D;
+  const float sl2 = a.scale * kLog2e;
+
+  const int n_items = a.direct ? a.n_tokens : a.header->n_items;
+  const int total = n_items * a.kv_heads;
+
+  for (int work = blockIdx.x; work < total; work += gridDim.x) {
+    const int item = work / a.kv_heads, kvh = work - item * a.kv_heads;
+    int token, kv_begin, kv_len, part;
+    load_item(a, item, token, kv_begin, kv_len, part);
+    const int* tbl = a.block_tables + __ldg(a.table_offset + __ldg(a.token_seq + token));
+    const T* kc = static_cast<const T*>(a.k_cache) + kvh * D;
+    const T* vc = static_cast<const T*>(a.v_cache) + kvh * D;
+
+    // Query fragments: rows g and g+8 of the (padded) 16 x D group matrix.
+    uint32_t qf[KS][4];
+    {
+      const T* qb = static_cast<const T*>(a.q) + (static_cast<size_t>(token) * a.q_heads + kvh * a.group) * D;
+      const bool v0 = g < a.group, v1 = g + 8 < a.group;
+      const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(g) * D);
+      const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(g + 8) * D);
+#pragma unroll
+      for (int s = 0; s < KS; ++s) {
+        qf[s][0] = v0 ? __ldg(q0 + s * 8 + c) : 0u;
+        qf[s][1] = v1 ? __ldg(q1 + s * 8 + c) : 0u;
+        qf[s][2] = v0 ? __ldg(q0 + s * 8 + 4 + c) : 0u;
+        qf[s][3] = v1 ? __ldg(q1 + s * 8 + 4 + c) : 0u;
+      }
+    }
+
+    const int n_tiles = (kv_len + kTileKeys - 1) / kTileKeys;
+    const int n_my = n_tiles > warp ? (n_tiles - warp + kDecodeWarps - 1) / kDecodeWarps : 0;
+
+    // Issues the copies of this warp's i-th tile into ring stage i % STAGES.
+    auto issue = [&](int i) {
+      const int t = warp + i * kDecodeWarps;
+      const uint32_t st = warp_smem + (i % STAGES) * S::kStageBytes;
+      const int chunk = lane % CH, r0 = lane / CH;
+#pragma unroll
+      for (int p = 0; p < PASSES; ++p) {
+        const int r = r0 + p * ROWS_PER_PASS;
+        const int rel = t * kTileKeys + r;
+        const bool valid = rel < kv_len;
+        int64_t off = 0;
+        if (valid) off = slot_of(tbl, kv_begin + rel, a.block_size, a.bs_log2) * kv_dim + chunk * 8;
+        const uint32_t dst = st + r * S::kRowBytes + ((chunk ^ (r & 7)) << 4);
+        cp_async16(dst, kc + off, valid ? 16 : 0);
+        cp_async16(dst + S::kTileBytes, vc + off, valid ? 16 : 0);
+      }
+    };
+
+    float o[2 * KS][4];
+#pragma unroll
+    for (int n = 0; n < 2 * KS; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+      if (i < n_my) issue(i);
+      cp_async_commit();
+    }
+
+    for (int i = 0; i < n_my; ++i) {
+      cp_async_wait<STAGES - 2>();
+      __syncwarp();
+      if (i + STAGES - 1 < n_my) issue(i + STAGES - 1);
+      cp_async_commit();
+
+      const uint32_t kst = warp_smem + (i % STAGES) * S::kStageBytes;
+      const uint32_t vst = kst + S::kTileBytes;
+      const int t = warp + i * kDecodeWarps;
+
+      // S = Q K^T for 16 keys: two n-tiles of 8 keys.
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const int mi = lane >> 3, r = lane & 7;
+        const int krow = ((mi >> 1) << 3) + r;
+        const uint32_t rowaddr = kst + krow * S::kRowBytes;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int chunk = 2 * ks + (mi & 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(rowaddr + ((chunk ^ (krow & 7)) << 4), b0, b1, b2, b3);
+          mma16816<T>(s[0], qf[ks], b0, b1);
+          mma16816<T>(s[1], qf[ks], b2, b3);
+        }
+      }
+      // Scale into the log2 domain and mask keys past the end of the item.
+      const int col0 = t * kTileKeys + 2 * c;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = col0 + 8 * j + (e & 1);
+          s[j][e] = col < kv_len ? s[j][e] * sl2 : -INFINITY;
+        }
+      }
+      float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+      float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      // Every tile holds at least one valid key, so the new maxima are finite.
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+      m0 = mn0;
+      m1 = mn1;
+      float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        s[j][0] = exp2f(s[j][0] - mn0);
+        s[j][1] = exp2f(s[j][1] - mn0);
+        s[j][2] = exp2f(s[j][2] - mn1);
+        s[j][3] = exp2f(s[j][3] - mn1);
+        ps0 += s[j][0] + s[j][1];
+        ps1 += s[j][2] + s[j][3];
+      }
+      l0 = l0 * al0 + ps0;
+      l1 = l1 * al1 + ps1;
+#pragma unroll
+      for (int n = 0; n < 2 * KS; ++n) {
+        o[n][0] *= al0;
+        o[n][1] *= al0;
+        o[n][2] *= al1;
+        o[n][3] *= al1;
+      }
+      // O += P V : P (16 heads x 16 keys) straight from the score registers.
+      uint32_t pa[4];
+      pa[0] = pack2<T>(s[0][0], s[0][1]);
+      pa[1] = pack2<T>(s[0][2], s[0][3]);
+      pa[2] = pack2<T>(s[1][0], s[1][1]);
+      pa[3] = pack2<T>(s[1][2], s[1][3]);
+      {
+        const int mi = lane >> 3, r = lane & 7;
+        const int vrow = ((mi & 1) << 3) + r;
+        const uint32_t rowaddr = vst + vrow * S::kRowBytes;
+#pragma unroll
+        for (int np = 0; np < KS; ++np) {
+          const int chunk = 2 * np + (mi >> 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(rowaddr + ((chunk ^ (vrow & 7)) << 4), b0, b1, b2, b3);
+          mma16816<T>(o[2 * np], pa, b0, b1);
+          mma16816<T>(o[2 * np + 1], pa, b2, b3);
+        }
+      }
+    }
+    cp_async_wait_all();
+    // Row denominators: each lane of a quad summed a quarter of the keys.
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncthreads();  // every warp is done with its ring; reuse it for the merge
+
+    float* sm_o = reinterpret_cast<float*>(smem_raw);
+    float* sm_m = sm_o + kDecodeWarps * 16 * S::kLdo;
+    float* sm_l = sm_m + kDecodeWarps * 16;
+    float* sm_w = sm_l + kDecodeWarps * 16;
+    if (c == 0) {
+      sm_m[warp * 16 + g] = m0;
+      sm_m[warp * 16 + g + 8] = m1;
+      sm_l[warp * 16 + g] = l0;
+      sm_l[warp * 16 + g + 8] = l1;
+    }
+#pragma unroll
+    for (int n = 0; n < 2 * KS; ++n) {
+      float* r0p = sm_o + (warp * 16 + g) * S::kLdo + n * 8 + 2 * c;
+      float* r1p = sm_o + (warp * 16 + g + 8) * S::kLdo + n * 8 + 2 * c;
+      *reinterpret_cast<float2*>(r0p) = make_float2(o[n][0], o[n][1]);
+      *reinterpret_cast<float2*>(r1p) = make_float2(o[n][2], o[n][3]);
+    }
+    __syncthreads();
+    merge_warps_and_store<T, true>(a, token, kvh * a.group, a.group, part, sm_m, sm_l, sm_o, S::kLdo, sm_w);
+    if (part >= 0) arrive_and_combine<T, true>(a, token, kvh, &sm_flag);
+    __syncthreads();
+  }
+}
+
+// ============================================================================
+// SIMT path: fp32 K/V (the 1e-5 parity configuration) and every geometry the
+// tensor-core path does not take (head_dim not 64/128, group > 16, block sizes
+// that are not powers of two).  head_dim <= 32 * DJ.
+// ============================================================================
+constexpr int kSimtHeadBatch = 8;
+
+template <typename T, int DJ>
+__global__ void __launch_bounds__(kDecodeThreads) decode_simt_kernel(const DecodeArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int sm_flag;
+  const int D = a.head_dim;
+  const int ldo = D + 1;
+  float* sm_q = reinterpret_cast<float*>(smem_raw);          // [8][D]
+  float* sm_o = sm_q + kSimtHeadBatch * D;                   // [4][16][ldo]
+  float* sm_m = sm_o + kDecodeWarps * 16 * ldo;              // [4][16]
+  float* sm_l = sm_m + kDecodeWarps * 16;
+  float* sm_w = sm_l + kDecodeWarps * 16;                    // [6][16]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_dim = a.kv_heads * D;
+
+  const int n_items = a.direct ? a.n_tokens : a.header->n_items;
+  const int total = n_items * a.kv_heads;
+
+  for (int work = blockIdx.x; work < total; work += gridDim.x) {
+    const int item = work / a.kv_heads, kvh = work - item * a.kv_heads;
+    int token, kv_begin, kv_len, part;
+    load_item(a, item, token, kv_begin, kv_len, part);
+    const int* tbl = a.block_tables + __ldg(a.table_offset + __ldg(a.token_seq + token));
+    const T* kc = static_cast<const T*>(a.k_cache) + kvh * D;
+    const T* vc = static_cast<const T*>(a.v_cache) + kvh * D;
+
+    for (int hb = 0; hb < a.group; hb += kSimtHeadBatch) {
+      const int rows = min(kSimtHeadBatch, a.group - hb);
+      const int head0 = kvh * a.group + hb;
+      const T* qb = static_cast<const T*>(a.q) + (static_cast<size_t>(token) * a.q_heads + head0) * D;
+      for (int i = threadIdx.x; i < rows * D; i += kDecodeThreads) sm_q[i] = Elem<T>::to_f32(qb[i]);
+      __syncthreads();
+
+      float m[kSimtHeadBatch], l[kSimtHeadBatch], acc[kSimtHeadBatch][DJ];
+#pragma unroll
+      for (int h = 0; h < kSimtHeadBatch; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.f;
+#pragma unroll
+        for (int j = 0; j < DJ; ++j) acc[h][j] = 0.f;
+      }
+      for (int rel = warp; rel < kv_len; rel += kDecodeWarps) {
+        const int64_t off = slot_of(tbl, kv_begin + rel, a.block_size, a.bs_log2) * kv_dim;
+        float kr[DJ], vr[DJ];
+#pragma unroll
+        for (int j = 0; j < DJ; ++j) {
+          const int d = lane + 32 * j;
+          kr[j] = d < D ? Elem<T>::to_f32(kc[off + d]) : 0.f;
+          vr[j] = d < D ? Elem<T>::to_f32(vc[off + d]) : 0.f;
+        }
+#pragma unroll
+        for (int h = 0; h < kSimtHeadBatch; ++h) {
+          if (h < rows) {
+            float p = 0.f;
+#pragma unroll
+            for (int j = 0; j < DJ; ++j) {
+              const int d = lane + 32 * j;
+              if (d < D) p += sm_q[h * D + d] * kr[j];
+            }
+            const float s = warp_sum(p) * a.scale;
+            const float mn = fmaxf(m[h], s);
+            const float al = expf(m[h] - mn);  // exp(-inf) = 0 on the first key
+            const float w = expf(s - mn);
+            l[h] = l[h] * al + w;
+#pragma unroll
+            for (int j = 0; j < DJ; ++j) acc[h][j] = acc[h][j] * al + w * vr[j];
+            m[h] = mn;
+          }
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < kSimtHeadBatch; ++h) {
+        if (h < rows) {
+          if (lane == 0) {
+            sm_m[warp * 16 + h] = m[h];
+            sm_l[warp * 16 + h] = l[h];
+          }
+#pragma unroll
+          for (int j = 0; j < DJ; ++j) {
+            const int d = lane + 32 * j;
+            if (d < D) sm_o[(warp * 16 + h) * ldo + d] = acc[h][j];
+          }
+        }
+      }
+      __syncthreads();
+      merge_warps_and_store<T, false>(a, token, head0, rows, part, sm_m, sm_l, sm_o, ldo, sm_w);
+    }
+    if (part >= 0) arrive_and_combine<T, false>(a, token, kvh, &sm_flag);
+    __syncthreads();
+  }
+}
+
+inline size_t simt_smem_bytes(int head_dim) {
+  return sizeof(float) * (static_cast<size_t>(kSimtHeadBatch) * head_dim + kDecodeWarps * 16 * (head_dim + 1) +
+                          2 * kDecodeWarps * 16 + (kDecodeWarps + 2) * 16);
+}
+
+}  // namespace pkv

@@ -1,0 +1,147 @@
+"""Device-side operators of the paged-KV path, named and shaped after llm-engine's
+launchers (include/engine/cuda_kernels.h:43-62) and called through the C ABI.
+
+Arguments are torch CUDA tensors (torch is used only for device memory and
+streams); element type is taken from the tensors: float16 (the reference's CUDA
+dtype), bfloat16 or float32.  Errors raise, as the reference launchers throw; there
+is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _lib
+
+_SUFFIX = {"torch.float16": "f16", "torch.bfloat16": "bf16", "torch.float32": "f32"}
+
+
+def _suffix(t) -> str:
+    try:
+        return _SUFFIX[str(t.dtype)]
+    except KeyError:
+        raise TypeError(f"unsupported KV element type {t.dtype}") from None
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("paged-KV operators take CUDA tensors; there is no CPU path")
+    if not t.is_contiguous():
+        raise ValueError("paged-KV operators take contiguous tensors")
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    return getattr(stream, "cuda_stream", stream)
+
+
+def launch_store_kv(k, v, slots, k_cache, v_cache, n_tokens: int, kv_dim: int, stream=None) -> None:
+    """k_cache[slots[t]] = k[t], v_cache[slots[t]] = v[t] (engine::launch_store_kv)."""
+    fn = f"pkv_append_{_suffix(k_cache)}"
+    st = getattr(_lib.lib(), fn)(_ptr(k), _ptr(v), _ptr(slots), _ptr(k_cache), _ptr(v_cache), n_tokens, kv_dim,
+                                 _stream(stream))
+    _lib.check(fn, st)
+
+
+def decode_workspace_bytes(n_tokens: int, q_heads: int, kv_heads: int, head_dim: int) -> int:
+    return int(_lib.lib().pkv_decode_workspace_bytes(n_tokens, q_heads, kv_heads, head_dim))
+
+
+def alloc_decode_workspace(n_tokens: int, q_heads: int, kv_heads: int, head_dim: int, device="cuda"):
+    """A uint8 CUDA tensor large enough for split-K at this step size (256-byte aligned)."""
+    import torch
+    n = decode_workspace_bytes(n_tokens, q_heads, kv_heads, head_dim)
+    return torch.empty(max(n, 256), dtype=torch.uint8, device=device)
+
+
+def launch_attention_decode(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,
+                            n_tokens: int, q_heads: int, kv_heads: int, head_dim: int, block_size: int,
+                            scale: float, stream=None, workspace=None) -> None:
+    """engine::launch_attention_decode; `workspace` (uint8 CUDA tensor) enables split-K."""
+    fn = f"pkv_decode_attn_{_suffix(k_cache)}"
+    ws_ptr = _ptr(workspace)
+    ws_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    st = getattr(_lib.lib(), fn)(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(table_offset),
+                                 _ptr(token_seq), _ptr(token_pos), _ptr(out), n_tokens, q_heads, kv_heads,
+                                 head_dim, block_size, C.c_float(scale), ws_ptr, ws_bytes, _stream(stream))
+    _lib.check(fn, st)
+
+
+# llm-engine keeps two names for the same operation, chosen by ENGINE_ATTN
+# (src/model/cuda/cuda_model.cu:554-557); both are one kernel here.
+launch_attention_decode_gqa = launch_attention_decode
+
+
+class DecodePlan:
+    """Split-K work list built once per step and shared by every layer's attention call."""
+
+    def __init__(self, n_tokens: int, q_heads: int, kv_heads: int, head_dim: int, workspace=None, device="cuda"):
+        import torch
+        self.n_tokens, self.q_heads, self.kv_heads, self.head_dim = n_tokens, q_heads, kv_heads, head_dim
+        self.workspace = workspace if workspace is not None else alloc_decode_workspace(
+            n_tokens, q_heads, kv_heads, head_dim, device)
+        nstage = int(_lib.lib().pkv_decode_plan_staging_bytes(n_tokens, kv_heads))
+        self.staging = torch.empty(max(nstage, 256), dtype=torch.uint8).pin_memory()
+        self.plan = _lib.DecodePlan()
+
+    def _ws(self):
+        return self.workspace.data_ptr(), self.workspace.numel()
+
+    def build_host(self, token_pos_host, stream=None) -> "DecodePlan":
+        """token_pos_host: int32 numpy array or CPU tensor of the packed tokens' positions."""
+        import numpy as np
+        pos = np.ascontiguousarray(token_pos_host, dtype=np.int32)
+        p, n = self._ws()
+        st = _lib.lib().pkv_decode_plan_host(pos.ctypes.data, self.n_tokens, self.q_heads, self.kv_heads,
+                                             self.head_dim, self.staging.data_ptr(), self.staging.numel(), p, n,
+                                             _stream(stream), C.byref(self.plan))
+        _lib.check("pkv_decode_plan_host", st)
+        return self
+
+    def build_device(self, token_pos, stream=None) -> "DecodePlan":
+        p, n = self._ws()
+        st = _lib.lib().pkv_decode_plan_device(_ptr(token_pos), self.n_tokens, self.q_heads, self.kv_heads,
+                                               self.head_dim, p, n, _stream(stream), C.byref(self.plan))
+        _lib.check("pkv_decode_plan_device", st)
+        return self
+
+    def attention(self, q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,
+                  block_size: int, scale: float, stream=None) -> None:
+        fn = f"pkv_decode_attn_planned_{_suffix(k_cache)}"
+        p, n = self._ws()
+        st = getattr(_lib.lib(), fn)(C.byref(self.plan), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                                     _ptr(table_offset), _ptr(token_seq), _ptr(token_pos), _ptr(out), block_size,
+                                     C.c_float(scale), p, n, _stream(stream))
+        _lib.check(fn, st)
+
+
+def launch_attention_prefill(q, k_cache, v_cache, block_tables, table_offset, q_start, q_len, ctx_len, out,
+                             n_seqs: int, max_q_len: int, q_heads: int, kv_heads: int, head_dim: int,
+                             block_size: int, num_blocks: int, scale: float, stream=None) -> None:
+    """Causal attention of each sequence's new chunk over its cached plus new tokens."""
+    fn = f"pkv_prefill_attn_{_suffix(k_cache)}"
+    st = getattr(_lib.lib(), fn)(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(table_offset),
+                                 _ptr(q_start), _ptr(q_len), _ptr(ctx_len), _ptr(out), n_seqs, max_q_len, q_heads,
+                                 kv_heads, head_dim, block_size, num_blocks, C.c_float(scale), _stream(stream))
+    _lib.check(fn, st)
+
+
+def launch_copy_blocks(k_cache, v_cache, src_dst_pairs, n_pairs: int, block_size: int, kv_dim: int,
+                       stream=None) -> None:
+    """Copy-on-write: block pairs[2i] -> block pairs[2i+1] in both pools."""
+    fn = f"pkv_copy_blocks_{_suffix(k_cache)}"
+    st = getattr(_lib.lib(), fn)(_ptr(k_cache), _ptr(v_cache), _ptr(src_dst_pairs), n_pairs, block_size, kv_dim,
+                                 _stream(stream))
+    _lib.check(fn, st)
+
+
+def launch_copy_blocks_layers(cache_ptrs, n_caches: int, src_dst_pairs, n_pairs: int, block_bytes: int,
+                              stream=None) -> None:
+    """Same for every pool at once; cache_ptrs is an int64 CUDA tensor of pool base addresses."""
+    st = _lib.lib().pkv_copy_blocks_layers(_ptr(cache_ptrs), n_caches, _ptr(src_dst_pairs), n_pairs, block_bytes,
+                                           _stream(stream))
+    _lib.check("pkv_copy_blocks_layers", st)
