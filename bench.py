@@ -204,7 +204,8 @@ def run_ours(args, rank, local_rank, world):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    w = wl.make(args.workload, seed=1234 + int(args.workload[-1]) + 1000 * rank)
+    sh = importlib.import_module("llm-engine_b200.sharding")
+    w = wl.make(args.workload, seed=sh.rank_seed(1234 + int(args.workload[-1]), rank), layers=args.layers)
     tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[w.dtype]
     bs, kv_dim, L = w.block_size, w.kv_dim, w.layers
     H = w.q_heads * w.head_dim
@@ -368,11 +369,13 @@ def run_ours(args, rank, local_rank, world):
                 "frac_of_nominal_8TBs": achieved / 8000.0}
 
     # ---- end to end ---------------------------------------------------------------------
-    ms_e2e = timed(step_e2e, args.steps, max(args.warmup, 3)) / args.steps
-    e2e_value = tokens_all / (ms_e2e * 1e-3)
-    ok = torch.equal(e_out, out)       # same inputs through both routes: identical bits
-    e2e = {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes),
-           "ms_per_step": ms_e2e, "matches_resident_output": bool(ok)}
+    e2e = None
+    if not args.no_e2e:
+        ms_e2e = timed(step_e2e, args.steps, max(args.warmup, 3)) / args.steps
+        e2e_value = tokens_all / (ms_e2e * 1e-3)
+        ok = torch.equal(e_out, out)       # same inputs through both routes: identical bits
+        e2e = {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes),
+               "ms_per_step": ms_e2e, "matches_resident_output": bool(ok)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -397,7 +400,8 @@ def run_ours(args, rank, local_rank, world):
             "config": {"workload": f"{args.workload}: {WORKLOAD_TEXT[args.workload]}", "tokens_per_step_per_gpu": N,
                        "layers": L, "sharding": "by sequence: each rank owns its pool and its batch, no collective",
                        "l2": f"per-step working set {algo_bytes * L / 1e9:.2f} GB across {L} distinct per-layer pools, far larger than the 126 MB L2",
-                       "launch": "cuda graph replay" if use_graph else "eager launches"},
+                       "launch": "cuda graph replay" if use_graph else "eager launches",
+                       **({"layers_override": args.layers} if args.layers else {})},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "step_hbm_gbs": (algo_bytes + w.append_bytes_per_layer()) * L / (ms_step * 1e-3) / 1e9,
@@ -416,6 +420,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling runs only; noted in config)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

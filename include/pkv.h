@@ -53,6 +53,13 @@ const char* pkv_status_string(int status);
 /* Detail of the calling thread's most recent failure ("" if none). */
 const char* pkv_last_error(void);
 
+/* Debugging aid, the one entry point that SYNCHRONISES the device: reads and clears
+ * the word in which kernels record a bounded wait that ran out (bit 0: a TMA
+ * producer never saw its ring slot released; bit 1: a consumer never saw its tile
+ * arrive; bit 2: a prefill pipeline wait).  0 means no kernel ever gave up.
+ * No llm-engine counterpart. */
+int pkv_debug_device_flags(unsigned int* flags);
+
 /* ------------------------------------------------------------------ a1 ----
  * K/V append.  Replaces engine::launch_store_kv (include/engine/cuda_kernels.h:43-45,
  * src/kernels/store_kv.cu:20-36) and the CPU memcpy pair
@@ -117,7 +124,7 @@ typedef struct pkv_decode_plan {
   int chunk;      /* keys per work item; 0 = no splitting */
   int n_items;    /* exact item count when host-built, upper bound when device-built */
   int exact;      /* 1 if n_items is exact */
-  int reserved;
+  int reserved;   /* internal: non-zero when some token was split */
 } pkv_decode_plan;
 
 size_t pkv_decode_plan_staging_bytes(int n_tokens, int kv_heads);

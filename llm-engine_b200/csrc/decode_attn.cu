@@ -1,10 +1,12 @@
 // C-ABI entry points for paged decode attention (include/pkv.h, section a2):
 // argument validation, split-K planning (host and device), kernel selection.
 #include <cstdlib>
+#include <type_traits>
 #include <cstring>
 #include <vector>
 
 #include "decode_attn.cuh"
+#include "decode_tma.cuh"
 #include "launch_util.hpp"
 #include "status.hpp"
 
@@ -17,6 +19,7 @@ struct Tuning {
   int wave_ctas;     // below this many blocks, smaller chunks are tried
   int forced_chunk;  // 0 = rule
   int variant;       // ring depth / occupancy variant of the tensor-core kernel
+  int use_tma;       // 1: TMA + warp-specialised kernel where the geometry allows (default)
   int max_extra_cap;
 };
 int env_int(const char* name, int dflt) {
@@ -31,6 +34,7 @@ const Tuning& tuning() {
     x.wave_ctas = env_int("PKV_DECODE_WAVE_CTAS", 592);
     x.forced_chunk = env_int("PKV_DECODE_CHUNK", 0);
     x.variant = env_int("PKV_DECODE_VARIANT", 0);
+    x.use_tma = env_int("PKV_DECODE_TMA", 1);
     x.max_extra_cap = 16384;
     return x;
   }();
@@ -158,6 +162,45 @@ int launch_mma(const DecodeArgs& a, int grid, cudaStream_t stream) {
   return check_launch("decode_mma_kernel");
 }
 
+int persistent_sms() {
+  static thread_local int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MINB>
+int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
+  using S = TmaSmem<D, MT, NSTAGES, WARPS>;
+  auto kern = decode_tma_kernel<T, D, NT, MT, NSTAGES, WARPS, MINB>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve %d bytes of shared memory: %s", S::kBytes, cudaGetErrorString(e));
+    configured_device = dev;
+  }
+  alignas(64) CUtensorMap kmap, vmap;
+  constexpr bool is_bf16 = !std::is_same<T, __half>::value;
+  const int kv_dim = a.kv_heads * a.head_dim;
+  int st = make_pool_tensor_map(&kmap, a.k_cache, is_bf16, kv_dim, 16, 1ull << 30);
+  if (st != PKV_OK) return st;
+  st = make_pool_tensor_map(&vmap, a.v_cache, is_bf16, kv_dim, 16, 1ull << 30);
+  if (st != PKV_OK) return st;
+  // `grid` counts work units; every warp is a worker and blocks are persistent:
+  // as many as can be resident, each warp striding through the unit list.
+  int blocks = (grid + WARPS - 1) / WARPS;
+  const int resident = persistent_sms() * MINB;
+  if (blocks > resident) blocks = resident;
+  kern<<<blocks, WARPS * 32, S::kBytes, stream>>>(a, kmap, vmap);
+  return check_launch("decode_tma_kernel");
+}
+
 template <typename T, int DJ>
 int launch_simt(const DecodeArgs& a, int grid, cudaStream_t stream) {
   const size_t smem = simt_smem_bytes(a.head_dim);
@@ -176,10 +219,38 @@ int launch_simt(const DecodeArgs& a, int grid, cudaStream_t stream) {
   return check_launch("decode_simt_kernel");
 }
 
+template <typename T, bool LOG2>
+int launch_combine(const DecodeArgs& a, cudaStream_t stream) {
+  if (a.direct) return PKV_OK;
+  long long blocks = static_cast<long long>(a.n_tokens) * a.kv_heads;
+  const long long cap = static_cast<long long>(persistent_sms()) * 16;
+  if (blocks > cap) blocks = cap;
+  decode_combine_kernel<T, LOG2><<<static_cast<int>(blocks), kCombineThreads, 0, stream>>>(a);
+  return check_launch("decode_combine_kernel");
+}
+
 template <typename T>
-int launch_decode(const DecodeArgs& a, int grid, cudaStream_t stream) {
+int launch_decode_main(const DecodeArgs& a, int grid, cudaStream_t stream, bool* log2_domain) {
+  *log2_domain = true;
   if constexpr (!IsF32<T>::value) {
     const bool mma_ok = (a.head_dim == 64 || a.head_dim == 128) && a.group <= 16 && a.bs_log2 >= 0;
+    const bool tma_ok = mma_ok && a.bs_log2 >= 4 && a.scale > 0.f && tuning().use_tma && tensor_map_encoder() != nullptr;
+    if (tma_ok) {
+      const int variant = tuning().variant;
+      if (a.head_dim == 64) {
+        if (a.group <= 8) {
+          if (variant == 1) return launch_tma<T, 64, 1, 1, 3, 4, 4>(a, grid, stream);
+          if (variant == 2) return launch_tma<T, 64, 1, 2, 2, 4, 3>(a, grid, stream);
+          if (variant == 3) return launch_tma<T, 64, 1, 2, 3, 4, 2>(a, grid, stream);
+          if (variant == 4) return launch_tma<T, 64, 1, 1, 6, 4, 2>(a, grid, stream);
+          if (variant == 5) return launch_tma<T, 64, 1, 1, 4, 8, 1>(a, grid, stream);
+          return launch_tma<T, 64, 1, 1, 4, 4, 3>(a, grid, stream);
+        }
+        return launch_tma<T, 64, 2, 1, 4, 4, 3>(a, grid, stream);
+      }
+      if (a.group <= 8) return launch_tma<T, 128, 1, 1, 3, 4, 2>(a, grid, stream);
+      return launch_tma<T, 128, 2, 1, 3, 4, 2>(a, grid, stream);
+    }
     if (mma_ok) {
       const int variant = tuning().variant;
       if (a.head_dim == 64) {
@@ -190,10 +261,20 @@ int launch_decode(const DecodeArgs& a, int grid, cudaStream_t stream) {
       return launch_mma<T, 128, 3, 2>(a, grid, stream);
     }
   }
+  *log2_domain = false;
   const int dj = (a.head_dim + 31) / 32;
   if (dj <= 2) return launch_simt<T, 2>(a, grid, stream);
   if (dj <= 4) return launch_simt<T, 4>(a, grid, stream);
   return launch_simt<T, 8>(a, grid, stream);
+}
+
+// Attention kernel, then (when the plan split any token) the merge of the partials.
+template <typename T>
+int launch_decode(const DecodeArgs& a, int grid, cudaStream_t stream, bool has_splits) {
+  bool log2_domain = true;
+  const int st = launch_decode_main<T>(a, grid, stream, &log2_domain);
+  if (st != PKV_OK || !has_splits) return st;
+  return log2_domain ? launch_combine<T, true>(a, stream) : launch_combine<T, false>(a, stream);
 }
 
 int validate_geometry(const char* fn, int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size) {
@@ -237,6 +318,7 @@ void fill_args(DecodeArgs& a, const void* q, const void* kc, const void* vc, con
   a.header = nullptr; a.items = nullptr; a.tok_split = nullptr; a.counters = nullptr;
   a.part_ml = nullptr; a.part_acc = nullptr;
   a.direct = 1;
+  a.debug = env_int("PKV_DECODE_DEBUG", 0);
 }
 
 void attach_workspace(DecodeArgs& a, void* workspace, const WsLayout& w) {
@@ -289,7 +371,7 @@ int plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, i
   plan->chunk = -1;                      // decided on the device
   plan->n_items = n_tokens + budget;     // upper bound
   plan->exact = 0;
-  plan->reserved = 0;
+  plan->reserved = 1;                    // tokens may have been split: run the merge
   return PKV_OK;
 }
 
@@ -314,7 +396,7 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
   long long blocks = static_cast<long long>(plan->n_items) * plan->kv_heads;
   if (!plan->exact && blocks > persistent_grid()) blocks = persistent_grid();
   if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
-  return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream));
+  return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream), plan->reserved != 0);
 }
 
 template <typename T>
@@ -332,7 +414,7 @@ int decode_all_in_one(const void* q, const void* kc, const void* vc, const int* 
     fill_args(a, q, kc, vc, bt, to, ts, tp, out, n_tokens, q_heads, kv_heads, head_dim, block_size, scale);
     long long blocks = static_cast<long long>(n_tokens) * kv_heads;
     if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
-    return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream));
+    return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream), false);
   }
   pkv_decode_plan plan;
   st = plan_device(tp, n_tokens, q_heads, kv_heads, head_dim, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), &plan);
@@ -346,6 +428,16 @@ int decode_all_in_one(const void* q, const void* kc, const void* vc, const int* 
 using namespace pkv;
 
 extern "C" {
+
+int pkv_debug_device_flags(unsigned int* flags) {
+  if (!flags) return fail(PKV_E_ARG, "pkv_debug_device_flags: null output");
+  unsigned int v = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_pkv_device_error, sizeof(v));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_pkv_device_error, &zero, sizeof(zero));
+  if (e != cudaSuccess) return fail(PKV_E_CUDA, "pkv_debug_device_flags: %s", cudaGetErrorString(e));
+  *flags = v;
+  return PKV_OK;
+}
 
 size_t pkv_decode_workspace_bytes(int n_tokens, int q_heads, int kv_heads, int head_dim) {
   if (n_tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0) return 0;
@@ -425,6 +517,7 @@ int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int 
   plan->chunk = chunk;
   plan->n_items = ni;
   plan->exact = 1;
+  plan->reserved = np > 0 ? 1 : 0;       // whether any token was split (the merge kernel is skipped otherwise)
   return PKV_OK;
 }
 

@@ -16,8 +16,8 @@
 //   * fp32 K/V, or any geometry the tensor-core path does not cover: a SIMT kernel
 //     with the same work decomposition and fp32 arithmetic throughout;
 //   * split-K: partial (max, denominator, accumulator) per item in the caller's
-//     workspace, merged by whichever thread block finishes a token's last item
-//     (an arrival counter per (token, kv head); nothing ever waits on a flag).
+//     workspace, merged by a small second kernel on the same stream; nothing ever
+//     waits on a flag.
 #pragma once
 
 #include "common.cuh"
@@ -45,6 +45,7 @@ struct DecodeArgs {
   float* part_ml;
   float* part_acc;
   int direct;  // 1: item i is token i over its whole history, no workspace
+  int debug;   // experiment switches (PKV_DECODE_DEBUG); 0 in normal use
 };
 
 constexpr int kDecodeThreads = 128;
@@ -66,10 +67,24 @@ template <bool LOG2> __device__ __forceinline__ float softmax_exp(float x) {
 // Merges the per-warp partial results of `rows` query heads (first one is
 // head0 of the token) held in shared memory and stores either the final output
 // rows or this item's split-K partial.
-//   sm_m, sm_l : [kDecodeWarps][16]      running max / denominator per warp and row
-//   sm_o       : [kDecodeWarps][16][ldo] unnormalised accumulators
-// Must be called by the whole block after a __syncthreads(); ends with one.
-template <typename T, bool LOG2>
+//   sm_m, sm_l : [kDecodeWarps][RS]      running max / denominator per warp and row
+//   sm_o       : [kDecodeWarps][RS][ldo] unnormalised accumulators   (RS = rows per warp, 8 or 16)
+// Must be called by every thread of the group `G` (the whole block, or the math
+// warps of a warp-specialised block) after a G::sync(); ends with one.
+struct BlockGroup {
+  static __device__ __forceinline__ void sync() { __syncthreads(); }
+  static __device__ __forceinline__ int size() { return blockDim.x; }
+  static __device__ __forceinline__ int tid() { return threadIdx.x; }
+};
+// The first kDecodeWarps warps of a block whose remaining warps do other work:
+// they meet on named barrier 1 and leave barrier 0 (__syncthreads) alone.
+struct MathWarpsGroup {
+  static __device__ __forceinline__ void sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+  static __device__ __forceinline__ int size() { return 128; }
+  static __device__ __forceinline__ int tid() { return threadIdx.x; }
+};
+
+template <typename T, bool LOG2, typename G = BlockGroup, int RS = 16>
 __device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int token, int head0, int rows, int part,
                                                       const float* sm_m, const float* sm_l, const float* sm_o,
                                                       int ldo, float* sm_w /*[kDecodeWarps+2][16]*/) {
@@ -78,25 +93,25 @@ __device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int t
   if (tid < rows) {
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) m = fmaxf(m, sm_m[w * 16 + tid]);
+    for (int w = 0; w < kDecodeWarps; ++w) m = fmaxf(m, sm_m[w * RS + tid]);
     float l = 0.f;
 #pragma unroll
     for (int w = 0; w < kDecodeWarps; ++w) {
-      const float mw = sm_m[w * 16 + tid];
+      const float mw = sm_m[w * RS + tid];
       const float f = (mw == -INFINITY) ? 0.f : softmax_exp<LOG2>(mw - m);
       sm_w[w * 16 + tid] = f;
-      l += f * sm_l[w * 16 + tid];
+      l += f * sm_l[w * RS + tid];
     }
     sm_w[kDecodeWarps * 16 + tid] = m;
     sm_w[(kDecodeWarps + 1) * 16 + tid] = l;
   }
-  __syncthreads();
+  G::sync();
   T* out = static_cast<T*>(a.out);
-  for (int idx = tid; idx < rows * D; idx += kDecodeThreads) {
+  for (int idx = tid; idx < rows * D; idx += G::size()) {
     const int r = idx / D, d = idx - r * D;
     float acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) acc += sm_w[w * 16 + r] * sm_o[(w * 16 + r) * ldo + d];
+    for (int w = 0; w < kDecodeWarps; ++w) acc += sm_w[w * 16 + r] * sm_o[(w * RS + r) * ldo + d];
     const int head = head0 + r;
     if (part < 0) {
       const float l = sm_w[(kDecodeWarps + 1) * 16 + r];
@@ -110,44 +125,93 @@ __device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int t
     ml[0] = sm_w[kDecodeWarps * 16 + tid];
     ml[1] = sm_w[(kDecodeWarps + 1) * 16 + tid];
   }
-  __syncthreads();
+  G::sync();
 }
 
-// Split-K arrival: after this block's partial for (token, kvh) is written, count
-// it; the block that completes the count merges all partials of the group's
-// heads into the output and resets the counter for the next launch that reuses
-// the plan.  No block ever waits for another.
+// Split-K merge.  A token whose history was cut into several work items has one
+// partial (running max, denominator, unnormalised accumulator) per item in the
+// workspace; this kernel, launched right after the attention kernel on the same
+// stream, folds them into the output rows.  Keeping the merge out of the attention
+// kernel keeps fences, atomics and dependent L2 round trips off its critical path.
+//
+// One thread block per (token, kv head) that was split, one thread per
+// (head, 4 dims).  The partials sit in L2 and a round trip costs several hundred
+// cycles, so a thread issues the loads of up to eight splits (max/denominator pair
+// and a 16-byte slice of the accumulator) before it touches any of them, and folds
+// batches together with the usual rescale.
+constexpr int kCombineThreads = 128;
+
 template <typename T, bool LOG2>
-__device__ __forceinline__ void arrive_and_combine(const DecodeArgs& a, int token, int kvh, int* sm_flag) {
-  const TokSplit ts = a.tok_split[token];
-  __threadfence();  // partial stores visible device-wide before the ticket is taken
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int ticket = atomicAdd(a.counters + token * a.kv_heads + kvh, 1);
-    *sm_flag = (ticket == ts.nsplits - 1);
-  }
-  __syncthreads();
-  if (!*sm_flag) return;
-  __threadfence();
+__global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecodeArgs a) {
   const int D = a.head_dim;
   T* out = static_cast<T*>(a.out);
-  const int head0 = kvh * a.group;
-  for (int idx = threadIdx.x; idx < a.group * D; idx += kDecodeThreads) {
-    const int r = idx / D, d = idx - r * D;
-    const int head = head0 + r;
-    float m = -INFINITY;
-    for (int s = 0; s < ts.nsplits; ++s)
-      m = fmaxf(m, __ldcg(a.part_ml + (static_cast<size_t>(ts.part_base + s) * a.q_heads + head) * 2));
-    float acc = 0.f, l = 0.f;
-    for (int s = 0; s < ts.nsplits; ++s) {
-      const size_t p = static_cast<size_t>(ts.part_base + s) * a.q_heads + head;
-      const float f = softmax_exp<LOG2>(__ldcg(a.part_ml + p * 2) - m);
-      l += f * __ldcg(a.part_ml + p * 2 + 1);
-      acc += f * __ldcg(a.part_acc + p * D + d);
+  constexpr int B = 8;
+  const int pairs = a.n_tokens * a.kv_heads;
+  for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
+    const int token = pr / a.kv_heads, kvh = pr - token * a.kv_heads;
+    const TokSplit ts = a.tok_split[token];
+    if (ts.nsplits <= 1) continue;
+    const int head0 = kvh * a.group;
+    if ((D & 3) == 0) {
+      const int D4 = D >> 2;
+      for (int idx = threadIdx.x; idx < a.group * D4; idx += kCombineThreads) {
+        const int r = idx / D4, d4 = idx - r * D4;
+        const int head = head0 + r;
+        float m_run = -INFINITY, l_run = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < ts.nsplits; s0 += B) {
+          float2 ml[B];
+          float4 v[B];
+#pragma unroll
+          for (int i = 0; i < B; ++i) {
+            if (s0 + i < ts.nsplits) {
+              const size_t p = static_cast<size_t>(ts.part_base + s0 + i) * a.q_heads + head;
+              ml[i] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + p * 2));
+              v[i] = __ldcg(reinterpret_cast<const float4*>(a.part_acc + p * D) + d4);
+            } else {
+              ml[i] = make_float2(-INFINITY, 0.f);
+              v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          float mb = m_run;
+#pragma unroll
+          for (int i = 0; i < B; ++i) mb = fmaxf(mb, ml[i].x);
+          const float f0 = (m_run == -INFINITY) ? 0.f : softmax_exp<LOG2>(m_run - mb);
+          l_run *= f0;
+          acc.x *= f0; acc.y *= f0; acc.z *= f0; acc.w *= f0;
+#pragma unroll
+          for (int i = 0; i < B; ++i) {
+            const float f = (ml[i].x == -INFINITY) ? 0.f : softmax_exp<LOG2>(ml[i].x - mb);
+            l_run += f * ml[i].y;
+            acc.x += f * v[i].x; acc.y += f * v[i].y; acc.z += f * v[i].z; acc.w += f * v[i].w;
+          }
+          m_run = mb;
+        }
+        const float inv = 1.f / l_run;
+        T* o = out + (static_cast<size_t>(token) * a.q_heads + head) * D + 4 * d4;
+        o[0] = Elem<T>::from_f32(acc.x * inv);
+        o[1] = Elem<T>::from_f32(acc.y * inv);
+        o[2] = Elem<T>::from_f32(acc.z * inv);
+        o[3] = Elem<T>::from_f32(acc.w * inv);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < a.group * D; idx += kCombineThreads) {
+        const int r = idx / D, d = idx - r * D;
+        const int head = head0 + r;
+        float m = -INFINITY;
+        for (int s = 0; s < ts.nsplits; ++s)
+          m = fmaxf(m, __ldcg(a.part_ml + (static_cast<size_t>(ts.part_base + s) * a.q_heads + head) * 2));
+        float acc = 0.f, l = 0.f;
+        for (int s = 0; s < ts.nsplits; ++s) {
+          const size_t p = static_cast<size_t>(ts.part_base + s) * a.q_heads + head;
+          const float f = softmax_exp<LOG2>(__ldcg(a.part_ml + p * 2) - m);
+          l += f * __ldcg(a.part_ml + p * 2 + 1);
+          acc += f * __ldcg(a.part_acc + p * D + d);
+        }
+        out[(static_cast<size_t>(token) * a.q_heads + head) * D + d] = Elem<T>::from_f32(acc / l);
+      }
     }
-    out[(static_cast<size_t>(token) * a.q_heads + head) * D + d] = Elem<T>::from_f32(acc / l);
   }
-  if (threadIdx.x == 0) a.counters[token * a.kv_heads + kvh] = 0;
 }
 
 __device__ __forceinline__ void load_item(const DecodeArgs& a, int item, int& token, int& kv_begin, int& kv_len, int& part) {
@@ -190,7 +254,6 @@ __global__ void __launch_bounds__(kDecodeThreads, MIN_BLOCKS) decode_mma_kernel(
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ int sm_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const uint32_t warp_smem = smem_u32(smem_raw) + warp * S::kWarpBytes;
@@ -368,8 +431,6 @@ __global__ void __launch_bounds__(kDecodeThreads, MIN_BLOCKS) decode_mma_kernel(
     }
     __syncthreads();
     merge_warps_and_store<T, true>(a, token, kvh * a.group, a.group, part, sm_m, sm_l, sm_o, S::kLdo, sm_w);
-    if (part >= 0) arrive_and_combine<T, true>(a, token, kvh, &sm_flag);
-    __syncthreads();
   }
 }
 
@@ -383,7 +444,6 @@ constexpr int kSimtHeadBatch = 8;
 template <typename T, int DJ>
 __global__ void __launch_bounds__(kDecodeThreads) decode_simt_kernel(const DecodeArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ int sm_flag;
   const int D = a.head_dim;
   const int ldo = D + 1;
   float* sm_q = reinterpret_cast<float*>(smem_raw);          // [8][D]
@@ -466,8 +526,6 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_simt_kernel(const Decod
       __syncthreads();
       merge_warps_and_store<T, false>(a, token, head0, rows, part, sm_m, sm_l, sm_o, ldo, sm_w);
     }
-    if (part >= 0) arrive_and_combine<T, false>(a, token, kvh, &sm_flag);
-    __syncthreads();
   }
 }
 

@@ -1,0 +1,367 @@
+// Paged decode attention, TMA variant (sm_100a): 16-bit K/V, head_dim 64 or 128,
+// GQA group <= 16, block_size a multiple of 16.
+//
+// Work unit = (token, key range) x kv head.  Every WARP is an independent worker:
+// it owns a private ring of shared-memory stages, fetches its own units, and
+// finishes them on its own -- there is no block-wide barrier and no cross-warp
+// merge anywhere in the kernel, so the look-ups at the start of a unit and the
+// store / split-K arrival at its end stall one warp out of the twelve or sixteen on
+// the SM while the others keep the memory system busy.
+//
+//   loads   one lane issues TMA box copies (cp.async.bulk.tensor.2d: 16 slots x 128
+//           bytes, 128-byte swizzle) through the block table, one box per 16 keys for
+//           K and for V, completing on the stage's mbarrier.  The issue pointer runs
+//           NSTAGES slabs ahead of the math and crosses unit boundaries, so the ring
+//           never drains between units.  Table entries are fetched 32 boxes at a
+//           time (one coalesced load) and handed out by shuffle.
+//   math    keys are the M dimension of mma.sync m16n8k16 and the group's query heads
+//           the N dimension (S^T = K Q^T, O^T = V^T P^T): a group of up to 8 heads
+//           wastes no tensor-core rows, and the online-softmax state of a head lives
+//           in the thread that owns its accumulator column -- no cross-lane traffic
+//           for the rescale, three shuffles per slab for the running maximum, one
+//           movmatrix per 8x8 block of P.
+//   finish  a unit that covers its token's whole history writes the output rows; any
+//           other writes its split-K partial, fire and forget; decode_combine_kernel
+//           (decode_attn.cuh) merges the partials afterwards.
+//
+// Every mbarrier wait is bounded; a wait that runs out records a flag in
+// g_pkv_device_error and the warp winds down instead of spinning.
+#pragma once
+
+#include "decode_attn.cuh"
+#include "tma_util.hpp"
+
+namespace pkv {
+
+__device__ unsigned int g_pkv_device_error = 0;
+constexpr unsigned kErrProducerWait = 1u, kErrConsumerWait = 2u;
+
+constexpr int kBoxBytes = 16 * 128;
+
+struct WarpGroup {
+  static __device__ __forceinline__ void sync() { __syncwarp(); }
+  static __device__ __forceinline__ int size() { return 32; }
+  static __device__ __forceinline__ int tid() { return threadIdx.x & 31; }
+};
+
+template <int D, int MT, int NSTAGES, int WARPS> struct TmaSmem {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kKBytes = MT * kHalves * kBoxBytes;  // K part of a stage; V follows
+  static constexpr int kStageBytes = 2 * kKBytes;
+  static constexpr int kWarpBytes = NSTAGES * kStageBytes;
+  static constexpr int kBytes = WARPS * kWarpBytes + 1024;
+};
+
+template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS>
+__global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
+    decode_tma_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap kmap,
+                      const __grid_constant__ CUtensorMap vmap) {
+  using S = TmaSmem<D, MT, NSTAGES, WARPS>;
+  constexpr int KS = D / 16;
+  constexpr int HALVES = S::kHalves;
+  constexpr int SLAB = 16 * MT;
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long full_bar[WARPS * NSTAGES];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const uint32_t ring0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t ring = ring0 + warp * S::kWarpBytes;
+  unsigned char* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+  const uint32_t bars = smem_u32(&full_bar[warp * NSTAGES]);
+  const float sl2 = a.scale * kLog2e;
+
+  // Once any warp has given up on a wait, later blocks do not start: the launch
+  // then ends within one wait limit instead of one per block.
+  if (*reinterpret_cast<volatile unsigned int*>(&g_pkv_device_error) != 0u) return;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < NSTAGES; ++s) mbar_init(bars + 8 * s, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+
+  const int n_items = a.direct ? a.n_tokens : a.header->n_items;
+  const int total = n_items * a.kv_heads;
+  const int gw = blockIdx.x * WARPS + warp, GW = gridDim.x * WARPS;
+
+  // ---------------------------- issue side ----------------------------
+  int iu = gw - GW;             // unit the issue pointer is in (advanced before first use)
+  int i_nslabs = 0, i_slab = 0, i_kvbeg = 0, i_len = 0, i_x0 = 0;
+  const int* i_tbl = nullptr;
+  int i_ent = 0, i_ent_base = -64;   // this lane's block-table entry for box i_ent_base + lane
+  uint32_t n_issued = 0, n_consumed = 0;
+
+  // Issues the next slab of this warp's unit sequence, if there is one.
+  auto issue_next = [&]() -> bool {
+    while (i_slab >= i_nslabs) {
+      iu += GW;
+      if (iu >= total) { iu = total; return false; }
+      const int item = iu / a.kv_heads, kvh = iu - item * a.kv_heads;
+      int token, part;
+      load_item(a, item, token, i_kvbeg, i_len, part);
+      i_tbl = a.block_tables + __ldg(a.table_offset + __ldg(a.token_seq + token));
+      i_nslabs = (i_len + SLAB - 1) / SLAB;
+      i_slab = 0;
+      i_x0 = kvh * D;
+      i_ent_base = -64;
+      // warm the query rows of this unit for the math side (group x D 16-bit values)
+      const char* qrow = reinterpret_cast<const char*>(static_cast<const T*>(a.q) +
+                                                       (static_cast<size_t>(token) * a.q_heads + kvh * a.group) * D);
+      if (lane * 128 < a.group * D * 2) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(qrow + lane * 128));
+    }
+    const int box0 = i_slab * MT;
+    if (box0 + MT > i_ent_base + 32) {   // fetch the entries of the next 32 boxes in one coalesced load
+      i_ent_base = box0;
+      const int rel = (box0 + lane) * 16;
+      i_ent = rel < i_len ? __ldg(i_tbl + ((i_kvbeg + rel) >> a.bs_log2)) : 0;
+    }
+    int ent[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) ent[m] = __shfl_sync(0xffffffffu, i_ent, box0 + m - i_ent_base);
+    // The slot's previous contents were read with ordinary loads (ldmatrix) by all
+    // lanes; order those before the asynchronous-proxy write that refills it.
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      const uint32_t slot = n_issued % NSTAGES;
+      const uint32_t fb = bars + 8 * slot;
+      const uint32_t st = ring + slot * S::kStageBytes;
+      const int rel0 = i_slab * SLAB;
+      int nvalid = 0;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) nvalid += (rel0 + 16 * m < i_len) ? 1 : 0;
+      mbar_arrive_expect_tx(fb, static_cast<uint32_t>(nvalid) * 2u * HALVES * kBoxBytes);
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (rel0 + 16 * m < i_len) {
+          const int key0 = i_kvbeg + rel0 + 16 * m;
+          const int y = (ent[m] << a.bs_log2) + (key0 & (a.block_size - 1));
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) {
+            const uint32_t dst = st + (m * HALVES + h) * kBoxBytes;
+            tma_load_2d(dst, &kmap, i_x0 + 64 * h, y, fb);
+            tma_load_2d(dst + S::kKBytes, &vmap, i_x0 + 64 * h, y, fb);
+          }
+        }
+      }
+    }
+    ++n_issued;
+    ++i_slab;
+    return true;
+  };
+
+  // ---------------------------- math side -----------------------------
+  const int mi = lane >> 3, r8 = lane & 7;
+  bool more = true;
+  for (int cu = gw; cu < total; cu += GW) {
+    const int item = cu / a.kv_heads, kvh = cu - item * a.kv_heads;
+    int token, kv_begin, kv_len, part;
+    load_item(a, item, token, kv_begin, kv_len, part);
+    const int n_slabs = (kv_len + SLAB - 1) / SLAB;
+
+    while (more && n_issued - n_consumed < NSTAGES) more = issue_next();
+
+    // Q^T fragments (B operand): rows = dims, columns = heads of the group.
+    uint32_t qb[KS][NT][2];
+    {
+      const T* qbase = static_cast<const T*>(a.q) + (static_cast<size_t>(token) * a.q_heads + kvh * a.group) * D;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int head = 8 * nt + g;
+        const bool hv = head < a.group;
+        const uint32_t* qrow = reinterpret_cast<const uint32_t*>(qbase + static_cast<size_t>(head) * D);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          qb[ks][nt][0] = hv ? __ldg(qrow + ks * 8 + c) : 0u;
+          qb[ks][nt][1] = hv ? __ldg(qrow + ks * 8 + 4 + c) : 0u;
+        }
+      }
+    }
+    float o[KS][NT][4];
+    float m_run[NT][2], l_run[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      m_run[nt][0] = m_run[nt][1] = -INFINITY;
+      l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+      for (int dm = 0; dm < KS; ++dm) o[dm][nt][0] = o[dm][nt][1] = o[dm][nt][2] = o[dm][nt][3] = 0.f;
+    }
+
+    bool ok = true;
+    for (int j = 0; j < n_slabs; ++j) {
+      while (more && n_issued - n_consumed < NSTAGES) more = issue_next();
+      const uint32_t slot = n_consumed % NSTAGES;
+      if (!mbar_wait(bars + 8 * slot, (n_consumed / NSTAGES) & 1u)) {
+        if (lane == 0) atomicOr(&g_pkv_device_error, kErrConsumerWait);
+        ok = false;
+        break;
+      }
+      const uint32_t kst = ring + slot * S::kStageBytes;
+      const uint32_t vst = kst + S::kKBytes;
+      const int rows_valid = min(SLAB, kv_len - j * SLAB);
+      if (rows_valid < SLAB) {
+        // Slots past the end of the history hold whatever was there before (or were
+        // never fetched): their scores are masked below, and their V rows are
+        // cleared here so that 0 * garbage cannot produce a NaN.
+        unsigned char* vptr = ring_ptr + slot * S::kStageBytes + S::kKBytes;
+        const int nrows = SLAB - rows_valid;
+        for (int i = lane; i < nrows * 8 * HALVES; i += 32) {
+          const int row = rows_valid + i / (8 * HALVES);
+          const int rem = i % (8 * HALVES);
+          const int h = rem >> 3, ch = rem & 7;
+          *reinterpret_cast<uint4*>(vptr + ((row >> 4) * HALVES + h) * kBoxBytes + (row & 15) * 128 + ch * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+      }
+
+      // S^T = K Q^T : MT m-tiles of 16 keys.
+      float s[MT][NT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) s[mt][nt][0] = s[mt][nt][1] = s[mt][nt][2] = s[mt][nt][3] = 0.f;
+        const int row16 = ((mi & 1) << 3) + r8;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int chunk = 2 * ks + (mi >> 1);
+          const uint32_t addr = kst + (mt * HALVES + (chunk >> 3)) * kBoxBytes + row16 * 128 + (((chunk & 7) ^ r8) << 4);
+          uint32_t ka[4];
+          ldmatrix_x4(addr, ka[0], ka[1], ka[2], ka[3]);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) mma16816<T>(s[mt][nt], ka, qb[ks][nt][0], qb[ks][nt][1]);
+        }
+      }
+      if (rows_valid < SLAB) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (16 * mt + g + 8 * (e >> 1) >= rows_valid) s[mt][nt][e] = -INFINITY;
+      }
+      // Online softmax, per head (thread holds heads 8nt+2c and 8nt+2c+1).
+      uint32_t pb[MT][NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float mx0 = fmaxf(s[0][nt][0], s[0][nt][2]);
+        float mx1 = fmaxf(s[0][nt][1], s[0][nt][3]);
+#pragma unroll
+        for (int mt = 1; mt < MT; ++mt) {
+          mx0 = fmaxf(mx0, fmaxf(s[mt][nt][0], s[mt][nt][2]));
+          mx1 = fmaxf(mx1, fmaxf(s[mt][nt][1], s[mt][nt][3]));
+        }
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+        const float al0 = exp2f((m_run[nt][0] - mn0) * sl2), al1 = exp2f((m_run[nt][1] - mn1) * sl2);
+        m_run[nt][0] = mn0;
+        m_run[nt][1] = mn1;
+        const float ng0 = -mn0 * sl2, ng1 = -mn1 * sl2;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const float p0 = exp2f(fmaf(s[mt][nt][0], sl2, ng0)), p1 = exp2f(fmaf(s[mt][nt][1], sl2, ng1));
+          const float p2 = exp2f(fmaf(s[mt][nt][2], sl2, ng0)), p3 = exp2f(fmaf(s[mt][nt][3], sl2, ng1));
+          ps0 += p0 + p2;
+          ps1 += p1 + p3;
+          // (key g | g+8 ; heads 2c, 2c+1)  ->  (head g ; keys 2c, 2c+1): the B operand of O^T += V^T P^T
+          movmatrix_trans(pb[mt][nt][0], pack2<T>(p0, p1));
+          movmatrix_trans(pb[mt][nt][1], pack2<T>(p2, p3));
+        }
+        l_run[nt][0] = l_run[nt][0] * al0 + ps0;
+        l_run[nt][1] = l_run[nt][1] * al1 + ps1;
+#pragma unroll
+        for (int dm = 0; dm < KS; ++dm) {
+          o[dm][nt][0] *= al0;
+          o[dm][nt][1] *= al1;
+          o[dm][nt][2] *= al0;
+          o[dm][nt][3] *= al1;
+        }
+      }
+      // O^T += V^T P^T : m-tiles of 16 dims, k = the slab's keys.
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row16 = ((mi >> 1) << 3) + r8;
+#pragma unroll
+        for (int dm = 0; dm < KS; ++dm) {
+          const int chunk = 2 * dm + (mi & 1);
+          const uint32_t addr = vst + (mt * HALVES + (chunk >> 3)) * kBoxBytes + row16 * 128 + (((chunk & 7) ^ r8) << 4);
+          uint32_t va[4];
+          ldmatrix_x4_trans(addr, va[0], va[1], va[2], va[3]);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) mma16816<T>(o[dm][nt], va, pb[mt][nt][0], pb[mt][nt][1]);
+        }
+      }
+      ++n_consumed;
+    }
+    if (!ok) return;  // this warp has copies in flight only into its own ring; nothing else depends on it
+
+    while (more && n_issued - n_consumed < NSTAGES) more = issue_next();  // keep loads flowing through the finish
+
+    // ------------------------------ finish the unit ------------------------------
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        l_run[nt][0] += __shfl_xor_sync(0xffffffffu, l_run[nt][0], off);
+        l_run[nt][1] += __shfl_xor_sync(0xffffffffu, l_run[nt][1], off);
+      }
+    }
+    const int head_base = kvh * a.group;
+    if (a.debug & 2) continue;
+    if (part < 0) {
+      T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.q_heads + head_base) * D;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int h0 = 8 * nt + 2 * c;
+        const float i0 = 1.f / l_run[nt][0], i1 = 1.f / l_run[nt][1];
+#pragma unroll
+        for (int dm = 0; dm < KS; ++dm) {
+          const int d = 16 * dm + g;
+          if (h0 < a.group) {
+            out[static_cast<size_t>(h0) * D + d] = Elem<T>::from_f32(o[dm][nt][0] * i0);
+            out[static_cast<size_t>(h0) * D + d + 8] = Elem<T>::from_f32(o[dm][nt][2] * i0);
+          }
+          if (h0 + 1 < a.group) {
+            out[static_cast<size_t>(h0 + 1) * D + d] = Elem<T>::from_f32(o[dm][nt][1] * i1);
+            out[static_cast<size_t>(h0 + 1) * D + d + 8] = Elem<T>::from_f32(o[dm][nt][3] * i1);
+          }
+        }
+      }
+    } else {
+      float* pacc = a.part_acc + (static_cast<size_t>(part) * a.q_heads + head_base) * D;
+      float* pml = a.part_ml + (static_cast<size_t>(part) * a.q_heads + head_base) * 2;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int h0 = 8 * nt + 2 * c;
+#pragma unroll
+        for (int dm = 0; dm < KS; ++dm) {
+          const int d = 16 * dm + g;
+          if (h0 < a.group) {
+            pacc[static_cast<size_t>(h0) * D + d] = o[dm][nt][0];
+            pacc[static_cast<size_t>(h0) * D + d + 8] = o[dm][nt][2];
+          }
+          if (h0 + 1 < a.group) {
+            pacc[static_cast<size_t>(h0 + 1) * D + d] = o[dm][nt][1];
+            pacc[static_cast<size_t>(h0 + 1) * D + d + 8] = o[dm][nt][3];
+          }
+        }
+        if (g == 0) {
+          if (h0 < a.group) { pml[2 * h0] = m_run[nt][0] * sl2; pml[2 * h0 + 1] = l_run[nt][0]; }
+          if (h0 + 1 < a.group) { pml[2 * h0 + 2] = m_run[nt][1] * sl2; pml[2 * h0 + 3] = l_run[nt][1]; }
+        }
+      }
+    }
+  }
+}
+
+}  // namespace pkv

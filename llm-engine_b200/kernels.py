@@ -145,3 +145,11 @@ def launch_copy_blocks_layers(cache_ptrs, n_caches: int, src_dst_pairs, n_pairs:
     st = _lib.lib().pkv_copy_blocks_layers(_ptr(cache_ptrs), n_caches, _ptr(src_dst_pairs), n_pairs, block_bytes,
                                            _stream(stream))
     _lib.check("pkv_copy_blocks_layers", st)
+
+
+def debug_device_flags() -> int:
+    """Reads and clears the word in which kernels record a bounded wait that ran out
+    (synchronises the device; 0 = no kernel ever gave up)."""
+    v = C.c_uint(0)
+    _lib.check("pkv_debug_device_flags", _lib.lib().pkv_debug_device_flags(C.byref(v)))
+    return int(v.value)

@@ -133,6 +133,7 @@ def check_case(case, pkv, torch, orc, mode, tol=None):
     assert np.array_equal(view(vcb), view(want_vc)), "V pool differs from the reference append"
     _, got = from_device(torch, orc, d["out"], case.dtype)
     assert np.isfinite(got).all()
+    assert pkv.debug_device_flags() == 0, "a kernel gave up on a bounded wait"
     e_ref, e_row = rel_errors(got.reshape(case.N * case.qh, case.hd), want_out.reshape(case.N * case.qh, case.hd))
     tol = tol or TOL[case.dtype]
     assert e_ref <= tol and e_row <= tol, f"{mode}: rel err {e_ref:.3e} (reference metric) / {e_row:.3e} (per row) > {tol}"
