@@ -362,7 +362,7 @@ def run_ours(args, rank, local_rank, world):
     peak, peak_src = peaks()
     algo_bytes = w.decode_bytes_per_layer()
     achieved = algo_bytes / (attn_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "decode_mma_kernel" if w.dtype != "f32" else "decode_simt_kernel",
+    roofline = {"bound": "hbm", "kernel": ("decode_tma_kernel + decode_combine_kernel" if w.dtype != "f32" else "decode_simt_kernel + decode_combine_kernel"),
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": algo_bytes,
                 "us_per_launch": attn_ms * 1e3, "launches_timed": len(evs),

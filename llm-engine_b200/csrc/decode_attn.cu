@@ -1,5 +1,6 @@
 // C-ABI entry points for paged decode attention (include/pkv.h, section a2):
 // argument validation, split-K planning (host and device), kernel selection.
+#include <algorithm>
 #include <cstdlib>
 #include <type_traits>
 #include <cstring>
@@ -31,7 +32,7 @@ const Tuning& tuning() {
   static const Tuning t = [] {
     Tuning x;
     x.target_ctas = env_int("PKV_DECODE_TARGET_CTAS", 4736);
-    x.wave_ctas = env_int("PKV_DECODE_WAVE_CTAS", 592);
+    x.wave_ctas = env_int("PKV_DECODE_WAVE_CTAS", 1776);  // workers (warps) resident on a 148-SM part
     x.forced_chunk = env_int("PKV_DECODE_CHUNK", 0);
     x.variant = env_int("PKV_DECODE_VARIANT", 0);
     x.use_tma = env_int("PKV_DECODE_TMA", 1);
@@ -239,12 +240,13 @@ int launch_decode_main(const DecodeArgs& a, int grid, cudaStream_t stream, bool*
       const int variant = tuning().variant;
       if (a.head_dim == 64) {
         if (a.group <= 8) {
+          // <T, head_dim, head tiles, 16-key tiles per stage, stages per warp, warps, blocks per SM>
           if (variant == 1) return launch_tma<T, 64, 1, 1, 3, 4, 4>(a, grid, stream);
-          if (variant == 2) return launch_tma<T, 64, 1, 2, 2, 4, 3>(a, grid, stream);
+          if (variant == 2) return launch_tma<T, 64, 1, 1, 4, 4, 3>(a, grid, stream);
           if (variant == 3) return launch_tma<T, 64, 1, 2, 3, 4, 2>(a, grid, stream);
-          if (variant == 4) return launch_tma<T, 64, 1, 1, 6, 4, 2>(a, grid, stream);
-          if (variant == 5) return launch_tma<T, 64, 1, 1, 4, 8, 1>(a, grid, stream);
-          return launch_tma<T, 64, 1, 1, 4, 4, 3>(a, grid, stream);
+          if (variant == 4) return launch_tma<T, 64, 1, 2, 2, 6, 2>(a, grid, stream);
+          if (variant == 5) return launch_tma<T, 64, 1, 2, 2, 7, 2>(a, grid, stream);
+          return launch_tma<T, 64, 1, 2, 2, 4, 3>(a, grid, stream);  // measured best on B200
         }
         return launch_tma<T, 64, 2, 1, 4, 4, 3>(a, grid, stream);
       }
@@ -318,7 +320,6 @@ void fill_args(DecodeArgs& a, const void* q, const void* kc, const void* vc, con
   a.header = nullptr; a.items = nullptr; a.tok_split = nullptr; a.counters = nullptr;
   a.part_ml = nullptr; a.part_acc = nullptr;
   a.direct = 1;
-  a.debug = env_int("PKV_DECODE_DEBUG", 0);
 }
 
 void attach_workspace(DecodeArgs& a, void* workspace, const WsLayout& w) {
@@ -486,25 +487,29 @@ int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int 
   TokSplit* tsp = reinterpret_cast<TokSplit*>(img + w.off_tok);
   WorkItem* it = reinterpret_cast<WorkItem*>(img + w.off_items);
   int ni = 0, np = 0;
-  // Full-size chunks first, ragged tails afterwards: thread blocks are handed out
-  // in index order, so the short items end up filling the last wave.
-  for (int pass = 0; pass < 2; ++pass) {
-    for (int t = 0; t < n_tokens; ++t) {
-      const int L = h_token_pos[t] + 1;
-      const int ns = chunk > 0 ? (L + chunk - 1) / chunk : 1;
-      if (pass == 0) {
-        tsp[t] = TokSplit{np, ns};
-        if (ns > 1) np += ns;
-      }
-      for (int s = 0; s < ns; ++s) {
-        const int b = chunk > 0 ? s * chunk : 0;
-        const int len = chunk > 0 ? (L - b < chunk ? L - b : chunk) : L;
-        const bool full = chunk > 0 && len == chunk;
-        if (full != (pass == 0)) continue;
-        it[ni++] = WorkItem{t, b, len, ns > 1 ? tsp[t].part_base + s : -1};
-      }
-    }
+  // Longest first: full-size chunks, then the ragged tails in decreasing length, so
+  // that dealing the list round-robin gives every worker about the same number of
+  // keys and the short units land at the end of the launch.  (Handing units out
+  // dynamically through an atomic counter was measured and was no faster.)
+  for (int t = 0; t < n_tokens; ++t) {
+    const int L = h_token_pos[t] + 1;
+    const int ns = chunk > 0 ? (L + chunk - 1) / chunk : 1;
+    tsp[t] = TokSplit{np, ns};
+    if (ns > 1) np += ns;
+    if (chunk > 0)
+      for (int s = 0; s + 1 < ns || (s < ns && L - s * chunk == chunk); ++s)
+        it[ni++] = WorkItem{t, s * chunk, chunk, ns > 1 ? tsp[t].part_base + s : -1};
   }
+  const int n_full = ni;
+  for (int t = 0; t < n_tokens; ++t) {
+    const int L = h_token_pos[t] + 1;
+    const int ns = tsp[t].nsplits;
+    const int b = chunk > 0 ? (ns - 1) * chunk : 0;
+    const int len = L - b;
+    if (chunk > 0 && len == chunk) continue;  // already listed as a full chunk
+    it[ni++] = WorkItem{t, b, len, ns > 1 ? tsp[t].part_base + ns - 1 : -1};
+  }
+  std::stable_sort(it + n_full, it + ni, [](const WorkItem& x, const WorkItem& y) { return x.kv_len > y.kv_len; });
   hd->magic = kPlanMagic;
   hd->n_items = ni;
   hd->chunk = chunk;

@@ -45,7 +45,6 @@ struct DecodeArgs {
   float* part_ml;
   float* part_acc;
   int direct;  // 1: item i is token i over its whole history, no workspace
-  int debug;   // experiment switches (PKV_DECODE_DEBUG); 0 in normal use
 };
 
 constexpr int kDecodeThreads = 128;
@@ -136,16 +135,17 @@ __device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int t
 //
 // One thread block per (token, kv head) that was split, one thread per
 // (head, 4 dims).  The partials sit in L2 and a round trip costs several hundred
-// cycles, so a thread issues the loads of up to eight splits (max/denominator pair
+// cycles, so a thread issues the loads of up to sixteen splits (max/denominator pair
 // and a 16-byte slice of the accumulator) before it touches any of them, and folds
 // batches together with the usual rescale.
 constexpr int kCombineThreads = 128;
+constexpr int kCombineBatch = 16;
 
 template <typename T, bool LOG2>
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecodeArgs a) {
   const int D = a.head_dim;
   T* out = static_cast<T*>(a.out);
-  constexpr int B = 8;
+  constexpr int B = kCombineBatch;
   const int pairs = a.n_tokens * a.kv_heads;
   for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
     const int token = pr / a.kv_heads, kvh = pr - token * a.kv_heads;

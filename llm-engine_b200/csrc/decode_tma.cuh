@@ -317,7 +317,6 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
       }
     }
     const int head_base = kvh * a.group;
-    if (a.debug & 2) continue;
     if (part < 0) {
       T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.q_heads + head_base) * D;
 #pragma unroll
