@@ -19,6 +19,8 @@ constexpr int kAppendThreads = 256;
 __global__ void __launch_bounds__(kAppendThreads) append_vec16_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v,
                                                                        const int* __restrict__ slots, uint4* __restrict__ k_cache,
                                                                        uint4* __restrict__ v_cache, long long total, int row_vecs) {
+  pdl_launch_dependents();
+  pdl_wait();
   // piece index -> (token, which pool, 16-byte piece of the row)
   for (long long i = blockIdx.x * static_cast<long long>(kAppendThreads) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * kAppendThreads) {
@@ -38,6 +40,8 @@ template <typename W>
 __global__ void __launch_bounds__(kAppendThreads) append_scalar_kernel(const W* __restrict__ k, const W* __restrict__ v,
                                                                         const int* __restrict__ slots, W* __restrict__ k_cache,
                                                                         W* __restrict__ v_cache, int kv_dim) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int token = blockIdx.x;
   const size_t src = static_cast<size_t>(token) * kv_dim, dst = static_cast<size_t>(slots[token]) * kv_dim;
   for (int d = threadIdx.x; d < kv_dim; d += kAppendThreads) {
@@ -58,13 +62,13 @@ int append_impl(const void* k, const void* v, const int* slots, void* k_cache, v
     const long long total = 2ll * n_tokens * row_vecs;
     long long blocks = (total + kAppendThreads - 1) / kAppendThreads;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    append_vec16_kernel<<<static_cast<int>(blocks), kAppendThreads, 0, s>>>(
-        static_cast<const uint4*>(k), static_cast<const uint4*>(v), slots, static_cast<uint4*>(k_cache),
-        static_cast<uint4*>(v_cache), total, row_vecs);
+    launch_pdl(append_vec16_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kAppendThreads), 0, s,
+               static_cast<const uint4*>(k), static_cast<const uint4*>(v), slots, static_cast<uint4*>(k_cache),
+               static_cast<uint4*>(v_cache), total, row_vecs);
     return check_launch("append_vec16_kernel");
   }
-  append_scalar_kernel<W><<<n_tokens, kAppendThreads, 0, s>>>(static_cast<const W*>(k), static_cast<const W*>(v), slots,
-                                                             static_cast<W*>(k_cache), static_cast<W*>(v_cache), kv_dim);
+  launch_pdl(append_scalar_kernel<W>, dim3(n_tokens), dim3(kAppendThreads), 0, s, static_cast<const W*>(k),
+             static_cast<const W*>(v), slots, static_cast<W*>(k_cache), static_cast<W*>(v_cache), kv_dim);
   return check_launch("append_scalar_kernel");
 }
 

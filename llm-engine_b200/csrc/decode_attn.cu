@@ -159,7 +159,7 @@ int launch_mma(const DecodeArgs& a, int grid, cudaStream_t stream) {
     if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve %d bytes of shared memory: %s", S::kBytes, cudaGetErrorString(e));
     configured_device = dev;
   }
-  kern<<<grid, kDecodeThreads, S::kBytes, stream>>>(a);
+  launch_pdl(kern, dim3(grid), dim3(kDecodeThreads), S::kBytes, stream, a);
   return check_launch("decode_mma_kernel");
 }
 
@@ -198,7 +198,7 @@ int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
   int blocks = (grid + WARPS - 1) / WARPS;
   const int resident = persistent_sms() * MINB;
   if (blocks > resident) blocks = resident;
-  kern<<<blocks, WARPS * 32, S::kBytes, stream>>>(a, kmap, vmap);
+  launch_pdl(kern, dim3(blocks), dim3(WARPS * 32), S::kBytes, stream, a, kmap, vmap);
   return check_launch("decode_tma_kernel");
 }
 
@@ -216,7 +216,7 @@ int launch_simt(const DecodeArgs& a, int grid, cudaStream_t stream) {
       configured_device = dev;
     }
   }
-  kern<<<grid, kDecodeThreads, smem, stream>>>(a);
+  launch_pdl(kern, dim3(grid), dim3(kDecodeThreads), smem, stream, a);
   return check_launch("decode_simt_kernel");
 }
 
@@ -226,7 +226,7 @@ int launch_combine(const DecodeArgs& a, cudaStream_t stream) {
   long long blocks = static_cast<long long>(a.n_tokens) * a.kv_heads;
   const long long cap = static_cast<long long>(persistent_sms()) * 16;
   if (blocks > cap) blocks = cap;
-  decode_combine_kernel<T, LOG2><<<static_cast<int>(blocks), kCombineThreads, 0, stream>>>(a);
+  launch_pdl(decode_combine_kernel<T, LOG2>, dim3(static_cast<unsigned>(blocks)), dim3(kCombineThreads), 0, stream, a);
   return check_launch("decode_combine_kernel");
 }
 

@@ -22,6 +22,7 @@
 
 #include "common.cuh"
 #include "decode_plan.hpp"
+#include "launch_util.hpp"
 
 namespace pkv {
 
@@ -143,6 +144,8 @@ constexpr int kCombineBatch = 16;
 
 template <typename T, bool LOG2>
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecodeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();  // the attention kernel's partials
   const int D = a.head_dim;
   T* out = static_cast<T*>(a.out);
   constexpr int B = kCombineBatch;
@@ -260,6 +263,8 @@ __global__ void __launch_bounds__(kDecodeThreads, MIN_BLOCKS) decode_mma_kernel(
   const int kv_dim = a.kv_heads * D;
   const float sl2 = a.scale * kLog2e;
 
+  pdl_launch_dependents();
+  pdl_wait();  // the pool rows appended by the preceding launch, the plan, the previous merge
   const int n_items = a.direct ? a.n_tokens : a.header->n_items;
   const int total = n_items * a.kv_heads;
 
@@ -454,6 +459,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_simt_kernel(const Decod
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_dim = a.kv_heads * D;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int n_items = a.direct ? a.n_tokens : a.header->n_items;
   const int total = n_items * a.kv_heads;
 

@@ -84,6 +84,11 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   }
   __syncwarp();
 
+  // Everything above touched only this block's shared memory.  From here on the
+  // kernel reads what earlier launches on the stream wrote (appended pool rows, the
+  // plan, the workspace the previous merge has finished with).
+  pdl_launch_dependents();
+  pdl_wait();
   const int n_items = a.direct ? a.n_tokens : a.header->n_items;
   const int total = n_items * a.kv_heads;
   const int gw = blockIdx.x * WARPS + warp, GW = gridDim.x * WARPS;
