@@ -159,19 +159,21 @@ int pkv_decode_attn_planned_f32(const pkv_decode_plan* plan, const void* q, cons
  * positions 0 .. ctx_len[s]+i (causal over cached plus new tokens).  K/V of the
  * chunk must already be in the pool (pkv_append_* first, as the reference orders
  * store_kv before attention, src/model/cuda/cuda_model.cu:362-368).
- * max_q_len >= max_s q_len[s] sizes the grid (the caller's chunk size,
- * include/engine/scheduler.h:26).  bf16 and f16, head_dim 64 or 128,
- * block_size a power of two in 8..128, q_heads % kv_heads == 0. */
+ * n_tokens is the total number of packed rows of q / out, num_blocks the pool size
+ * (both bound the TMA descriptors); max_q_len >= max_s q_len[s] sizes the grid (the
+ * caller's chunk size, include/engine/scheduler.h:26).  bf16 and f16, head_dim 64,
+ * block_size a power of two >= 16, q_heads % kv_heads == 0; other geometries return
+ * PKV_E_UNSUPPORTED (such steps go through pkv_decode_attn_*, as in the reference). */
 int pkv_prefill_attn_bf16(const void* q, const void* k_cache, const void* v_cache,
                           const int* block_tables, const int* table_offset, const int* q_start,
-                          const int* q_len, const int* ctx_len, void* out, int n_seqs, int max_q_len,
-                          int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks,
-                          float scale, pkv_stream stream);
+                          const int* q_len, const int* ctx_len, void* out, int n_tokens, int n_seqs,
+                          int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
+                          int num_blocks, float scale, pkv_stream stream);
 int pkv_prefill_attn_f16(const void* q, const void* k_cache, const void* v_cache,
                          const int* block_tables, const int* table_offset, const int* q_start,
-                         const int* q_len, const int* ctx_len, void* out, int n_seqs, int max_q_len,
-                         int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks,
-                         float scale, pkv_stream stream);
+                         const int* q_len, const int* ctx_len, void* out, int n_tokens, int n_seqs,
+                         int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
+                         int num_blocks, float scale, pkv_stream stream);
 
 /* ------------------------------------------------------------------ a5 ----
  * Prefix-cache copy-on-write block copy.  No llm-engine counterpart (it shares

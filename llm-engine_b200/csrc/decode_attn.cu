@@ -12,6 +12,7 @@
 #include "status.hpp"
 
 namespace pkv {
+int prefill_read_flags(unsigned int* flags);  // prefill_attn.cu
 namespace {
 
 // ---- tuning knobs (read once) ---------------------------------------------------
@@ -436,7 +437,10 @@ int pkv_debug_device_flags(unsigned int* flags) {
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_pkv_device_error, sizeof(v));
   if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_pkv_device_error, &zero, sizeof(zero));
   if (e != cudaSuccess) return fail(PKV_E_CUDA, "pkv_debug_device_flags: %s", cudaGetErrorString(e));
-  *flags = v;
+  unsigned int pf = 0;
+  const int st = pkv::prefill_read_flags(&pf);
+  if (st != PKV_OK) return st;
+  *flags = v | pf;
   return PKV_OK;
 }
 

@@ -1,14 +1,472 @@
-// Paged (chunked) prefill attention entry points (include/pkv.h, section a3).
+// Paged (chunked) prefill attention on the 5th-generation tensor cores (sm_100a):
+// entry points of include/pkv.h, section a3.
+//
+// llm-engine has no prefill kernel (src/kernels/attention_prefill.cu:1 is a stub):
+// every prompt token goes through the decode kernel and re-reads its whole history.
+// Here a thread block takes 128 consecutive tokens of one sequence's chunk for one
+// query head and walks the keys in tiles of 128, so S = Q K^T and O = P V are dense
+// 128 x 128 x 64 contractions issued as tcgen05.mma with the accumulators in tensor
+// memory.  The result it must agree with is ref::paged_attention_head
+// (include/engine/ops.h:87-111) applied to every (token, head) of the chunk.
+//
+// Roles inside a block of 192 threads:
+//   warp 4 (one lane)   TMA producer: the Q tile once, then per key tile eight boxes of
+//                       16 slots x 128 bytes for K and eight for V, gathered through the
+//                       block table into a two-stage ring (128-byte swizzle, which is
+//                       also the canonical shared-memory layout of the MMA operands).
+//   warp 5 (one lane)   MMA issuer: S[j] = Q K_j^T (4 MMAs of K=16) into one of two S
+//                       buffers in tensor memory, then O_j = P_j V_j (8 MMAs) into one of
+//                       two O-tile buffers; tcgen05.commit signals the mbarriers.
+//   warps 0-3           softmax: thread r owns row r (tensor-memory lane r).  Two passes
+//                       over S with tcgen05.ld (row max, then exp2 / row sum / P written
+//                       to shared memory as bf16 in the operand layout), causal mask by
+//                       absolute position; the running output lives in registers and
+//                       each O tile is folded in with the usual rescale, so tensor
+//                       memory is never read-modify-written.
+// S[j+1] is issued before P_j V_j, so the tensor core works on the next scores while
+// the softmax warps are busy with the current ones.
+//
+// Every mbarrier wait is bounded: a wait that runs out sets bit 2 of the device error
+// word and the block carries on to its tear-down (tensor memory is always released).
+#include <type_traits>
+
+#include "common.cuh"
 #include "launch_util.hpp"
 #include "status.hpp"
+#include "tma_util.hpp"
+
+namespace pkv {
+
+__device__ unsigned int g_pkv_prefill_error = 0;
+
+namespace {
+
+constexpr int kQTile = 128;     // query rows per block
+constexpr int kKTile = 128;     // keys per tile
+constexpr int kHd = 64;         // head_dim this kernel is written for
+constexpr int kThreads = 192;
+constexpr int kTileBytes = 128 * 128;            // 128 rows x 128 bytes
+constexpr int kBox = 16 * 128;                   // one TMA box: 16 slots x 128 bytes
+constexpr int kSmemQ = 0;
+constexpr int kSmemKV = kSmemQ + kTileBytes;     // 2 stages x (K, V)
+constexpr int kSmemP = kSmemKV + 4 * kTileBytes; // 2 buffers x 2 blocks of 64 keys
+constexpr int kSmemTotal = kSmemP + 4 * kTileBytes + 1024;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemS = 0, kTmemO = 256;     // S0 @0, S1 @128, O0 @256, O1 @320
+
+struct PrefillArgs {
+  const int* block_tables;
+  const int* table_offset;
+  const int* q_start;
+  const int* q_len;
+  const int* ctx_len;
+  void* out;
+  int q_heads, kv_heads, group;
+  int block_size, bs_log2;
+  float scale;
+};
+
+// ---- tcgen05 wrappers -----------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes packed 8 to a
+// 1024-byte group (stride-dimension offset 1024): the layout TMA writes and the
+// canonical layout of both K-major operands (Q, K, P) and the MN-major one (V).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>(1u) << 16;             // leading-dimension offset (unused with this swizzle)
+  d |= static_cast<uint64_t>(1024u >> 4) << 32;     // stride-dimension offset: next group of 8 rows
+  d |= static_cast<uint64_t>(1u) << 46;             // descriptor version of this architecture
+  d |= static_cast<uint64_t>(2u) << 61;             // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16, fp32 accumulate, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(bool bf16, int n, bool b_mn_major) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ void give_up() { atomicOr(&g_pkv_prefill_error, 4u); }
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+    prefill_tc_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap qmap,
+                      const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr uint32_t kIdescQK = instr_desc(kBf16, kKTile, false);
+  constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd, true);
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[15];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sP = base + kSmemP;
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, S_EMPTY = 7, P_FULL = 9, PV_DONE = 11, O_EMPTY = 13 };
+
+  // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
+  if (threadIdx.x == 0) {
+    mbar_init(BAR(Q_FULL), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(BAR(KV_FULL + i), 1);
+      mbar_init(BAR(KV_EMPTY + i), 1);   // arrived by tcgen05.commit after P_j V_j
+      mbar_init(BAR(S_FULL + i), 1);     // tcgen05.commit after Q K_j^T
+      mbar_init(BAR(S_EMPTY + i), 128);  // every softmax thread, after its last read of S
+      mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P
+      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O tile ready, P buffer free
+      mbar_init(BAR(O_EMPTY + i), 128);  // every softmax thread, after reading the O tile
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int seq = blockIdx.z;
+  const int head = blockIdx.x;
+  const int q_len = __ldg(a.q_len + seq);
+  const int n_qtiles = (q_len + kQTile - 1) / kQTile;
+  const int tile = n_qtiles - 1 - static_cast<int>(blockIdx.y);  // longest key ranges first
+  const bool active = tile >= 0;                                 // uniform for the whole block
+  const int ctx = __ldg(a.ctx_len + seq);
+  const int row0 = __ldg(a.q_start + seq) + tile * kQTile;       // first packed row of this tile
+  const int rows_here = min(kQTile, q_len - tile * kQTile);
+  const int kv_total = ctx + tile * kQTile + rows_here;          // keys 0 .. kv_total-1 are visible to the tile
+  const int n_kt = active ? (kv_total + kKTile - 1) / kKTile : 0;
+  const int kvh = head / a.group;
+  // After a wait has run out (here or in an earlier block of this launch) no further
+  // wait spins: the block falls through its schedule and releases its tensor memory.
+  bool dead = *reinterpret_cast<volatile unsigned int*>(&g_pkv_prefill_error) != 0u;
+  auto WAIT = [&](uint32_t bar, uint32_t parity) {
+    if (dead) return;
+    if (!mbar_wait(bar, parity)) {
+      dead = true;
+      give_up();
+    }
+  };
+
+  if (!active) {
+    // nothing to do for this tile index; fall through to the tear-down
+  } else if (warp == 4) {
+    // ================================ TMA producer ================================
+    const int* tbl = a.block_tables + __ldg(a.table_offset + seq);
+    if (lane == 0) {
+      mbar_arrive_expect_tx(BAR(Q_FULL), kTileBytes);
+      tma_load_2d(sQ, &qmap, head * kHd, row0, BAR(Q_FULL));
+    }
+    for (int j = 0; j < n_kt; ++j) {
+      const int st = j & 1;
+      const int rel = j * kKTile + (lane & 7) * 16;
+      int ent = 0;
+      if (rel < kv_total) ent = __ldg(tbl + (rel >> a.bs_log2));
+      int y[8];
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        const int e = __shfl_sync(0xffffffffu, ent, b);
+        y[b] = (e << a.bs_log2) + ((j * kKTile + 16 * b) & (a.block_size - 1));
+      }
+      if (lane == 0) {
+        WAIT(BAR(KV_EMPTY + st), ((j >> 1) & 1) ^ 1);
+        int nvalid = 0;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) nvalid += (j * kKTile + 16 * b < kv_total) ? 1 : 0;
+        mbar_arrive_expect_tx(BAR(KV_FULL + st), static_cast<uint32_t>(nvalid) * 2u * kBox);
+        const uint32_t kdst = sKV + st * 2 * kTileBytes, vdst = kdst + kTileBytes;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          if (j * kKTile + 16 * b < kv_total) {
+            tma_load_2d(kdst + b * kBox, &kmap, kvh * kHd, y[b], BAR(KV_FULL + st));
+            tma_load_2d(vdst + b * kBox, &vmap, kvh * kHd, y[b], BAR(KV_FULL + st));
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == 5) {
+    // ================================ MMA issuer ================================
+    if (lane == 0) {
+      WAIT(BAR(Q_FULL), 0);
+      auto issue_qk = [&](int j) {
+        const int st = j & 1;
+        WAIT(BAR(KV_FULL + st), (j >> 1) & 1);
+        WAIT(BAR(S_EMPTY + st), ((j >> 1) & 1) ^ 1);
+        tc_fence_after();
+        const uint32_t ks_base = sKV + st * 2 * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kHd / 16; ++ks)
+          tc_mma(tmem + kTmemS + st * 128, smem_desc(sQ + ks * 32), smem_desc(ks_base + ks * 32), kIdescQK, ks > 0);
+        tc_commit(BAR(S_FULL + st));
+      };
+      issue_qk(0);
+      for (int j = 0; j < n_kt; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_kt) issue_qk(j + 1);
+        WAIT(BAR(P_FULL + st), (j >> 1) & 1);
+        WAIT(BAR(O_EMPTY + st), ((j >> 1) & 1) ^ 1);
+        tc_fence_after();
+        const uint32_t v_base = sKV + st * 2 * kTileBytes + kTileBytes;
+        const uint32_t p_base = sP + st * 2 * kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kKTile / 16; ++kk)
+          tc_mma(tmem + kTmemO + st * 64, smem_desc(p_base + (kk >> 2) * kTileBytes + (kk & 3) * 32),
+                 smem_desc(v_base + kk * 2048), kIdescPV, kk > 0);
+        tc_commit(BAR(KV_EMPTY + st));
+        tc_commit(BAR(PV_DONE + st));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================================ softmax warps ================================
+    const int r = threadIdx.x;                      // row of the tile == tensor-memory lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int limit = ctx + tile * kQTile + min(r, rows_here - 1);   // last visible key position of this row
+    const float sl2 = a.scale * kLog2e;
+    float o[kHd];
+#pragma unroll
+    for (int d = 0; d < kHd; ++d) o[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    auto fold_o_tile = [&](int jj) {   // o += O tile of key tile jj
+      const int st = jj & 1;
+      WAIT(BAR(PV_DONE + st), (jj >> 1) & 1);
+      tc_fence_after();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[32];
+        tc_ld32(tmem + lane_addr + kTmemO + st * 64 + h * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[h * 32 + i] += __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(BAR(O_EMPTY + st));
+    };
+
+    for (int j = 0; j < n_kt; ++j) {
+      const int st = j & 1;
+      const int k0 = j * kKTile;
+      WAIT(BAR(S_FULL + st), (j >> 1) & 1);
+      tc_fence_after();
+      const bool masked = k0 + kKTile - 1 > limit;
+      // pass 1: row maximum (raw scores; the scale is positive, so it commutes with max)
+      float mx = -INFINITY;
+#pragma unroll
+      for (int cblk = 0; cblk < 4; ++cblk) {
+        uint32_t v[32];
+        tc_ld32(tmem + lane_addr + kTmemS + st * 128 + cblk * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (masked && k0 + cblk * 32 + i > limit) s = -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);          // finite: key 0 is visible to every row
+      const float alpha = exp2f((m_run - m_new) * sl2);
+      const float neg = -m_new * sl2;
+      m_run = m_new;
+      // the P buffer is free once P_{j-2} V_{j-2} has completed
+      WAIT(BAR(PV_DONE + st), ((j >> 1) & 1) ^ 1);
+      // pass 2: p = exp2(s * scale * log2e - m), row sum, P to shared memory in operand layout
+      float psum = 0.f;
+      unsigned char* prow = base_ptr + kSmemP + st * 2 * kTileBytes + r * 128;
+#pragma unroll
+      for (int cblk = 0; cblk < 4; ++cblk) {
+        uint32_t v[32];
+        tc_ld32(tmem + lane_addr + kTmemS + st * 128 + cblk * 32, v);
+        tc_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
+          if (masked && k0 + cblk * 32 + i > limit) s0 = -INFINITY;
+          if (masked && k0 + cblk * 32 + i + 1 > limit) s1 = -INFINITY;
+          const float p0 = exp2f(fmaf(s0, sl2, neg)), p1 = exp2f(fmaf(s1, sl2, neg));
+          psum += p0 + p1;
+          packed[i >> 1] = pack2<T>(p0, p1);
+        }
+        // 32 keys = 4 chunks of 16 bytes; keys 0-63 live in block 0 of the buffer, 64-127 in block 1
+        unsigned char* blk = prow + (cblk >> 1) * kTileBytes;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (cblk & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(blk + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(BAR(S_EMPTY + st));                // S buffer may be overwritten by Q K_{j+2}^T
+      l_run = l_run * alpha + psum;
+      if (j == n_kt - 1 && kv_total - k0 < kKTile) {
+        // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
+        // behind them are whatever the pool or the ring held; clear them so 0 * x stays 0.
+        WAIT(BAR(KV_FULL + st), (j >> 1) & 1);
+        if (r >= kv_total - k0) {
+          unsigned char* vrow = base_ptr + kSmemKV + st * 2 * kTileBytes + kTileBytes + r * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vrow + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // P (and V) stores before the MMA reads them
+      mbar_arrive(BAR(P_FULL + st));
+      if (j > 0) fold_o_tile(j - 1);
+#pragma unroll
+      for (int d = 0; d < kHd; ++d) o[d] *= alpha;
+    }
+    fold_o_tile(n_kt - 1);
+    if (r < rows_here) {
+      const float inv = 1.f / l_run;
+      T* orow = static_cast<T*>(a.out) + (static_cast<size_t>(row0 + r) * a.q_heads + head) * kHd;
+#pragma unroll
+      for (int d = 0; d < kHd; d += 8) {
+        uint4 w;
+        w.x = pack2<T>(o[d] * inv, o[d + 1] * inv);
+        w.y = pack2<T>(o[d + 2] * inv, o[d + 3] * inv);
+        w.z = pack2<T>(o[d + 4] * inv, o[d + 5] * inv);
+        w.w = pack2<T>(o[d + 6] * inv, o[d + 7] * inv);
+        *reinterpret_cast<uint4*>(orow + d) = w;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+int log2_exact(int x) {
+  if (x <= 0 || (x & (x - 1))) return -1;
+  int l = 0;
+  while ((1 << l) < x) ++l;
+  return l;
+}
+
+template <typename T>
+int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                 const int* table_offset, const int* q_start, const int* q_len, const int* ctx_len, void* out,
+                 int n_tokens, int n_seqs, int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
+                 int num_blocks, float scale, pkv_stream stream) {
+  const char* fn = "pkv_prefill_attn";
+  if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return PKV_OK;
+  if (!q || !k_cache || !v_cache || !block_tables || !table_offset || !q_start || !q_len || !ctx_len || !out)
+    return fail(PKV_E_ARG, "%s: null device pointer", fn);
+  if (q_heads <= 0 || kv_heads <= 0 || num_blocks <= 0)
+    return fail(PKV_E_ARG, "%s: q_heads %d, kv_heads %d, num_blocks %d must be > 0", fn, q_heads, kv_heads, num_blocks);
+  if (q_heads % kv_heads != 0)
+    return fail(PKV_E_UNSUPPORTED, "%s: q_heads %d is not a multiple of kv_heads %d", fn, q_heads, kv_heads);
+  if (head_dim != kHd)
+    return fail(PKV_E_UNSUPPORTED, "%s: head_dim %d; the tensor-core kernel is written for head_dim %d", fn, head_dim, kHd);
+  const int bsl = log2_exact(block_size);
+  if (bsl < 4)
+    return fail(PKV_E_UNSUPPORTED, "%s: block_size %d; needs a power of two >= 16 (one TMA box is 16 slots)", fn, block_size);
+  if (!(scale > 0.f)) return fail(PKV_E_ARG, "%s: scale must be positive", fn);
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
+    return fail(PKV_E_ARG, "%s: q, out and the K/V pools must be 16-byte aligned", fn);
+  if (n_seqs > 65535) return fail(PKV_E_UNSUPPORTED, "%s: at most 65535 sequences per call", fn);
+  PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+  if (!enc) return fail(PKV_E_CUDA, "%s: cuTensorMapEncodeTiled is not available from this driver", fn);
+
+  constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+  alignas(64) CUtensorMap qmap, kmap, vmap;
+  const int kv_dim = kv_heads * head_dim;
+  int st = make_pool_tensor_map(&kmap, k_cache, is_bf16, kv_dim, 16, static_cast<uint64_t>(num_blocks) * block_size);
+  if (st != PKV_OK) return st;
+  st = make_pool_tensor_map(&vmap, v_cache, is_bf16, kv_dim, 16, static_cast<uint64_t>(num_blocks) * block_size);
+  if (st != PKV_OK) return st;
+  // q as [n_tokens][q_heads*head_dim]; rows past n_tokens read as zeros
+  st = make_pool_tensor_map(&qmap, q, is_bf16, q_heads * head_dim, kQTile, static_cast<uint64_t>(n_tokens));
+  if (st != PKV_OK) return st;
+
+  auto kern = prefill_tc_kernel<T>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: cannot reserve %d bytes of shared memory: %s", fn, kSmemTotal, cudaGetErrorString(e));
+    configured_device = dev;
+  }
+  PrefillArgs a;
+  a.block_tables = block_tables; a.table_offset = table_offset;
+  a.q_start = q_start; a.q_len = q_len; a.ctx_len = ctx_len;
+  a.out = out;
+  a.q_heads = q_heads; a.kv_heads = kv_heads; a.group = q_heads / kv_heads;
+  a.block_size = block_size; a.bs_log2 = bsl;
+  a.scale = scale;
+  const dim3 grid(q_heads, (max_q_len + kQTile - 1) / kQTile, n_seqs);
+  launch_pdl(kern, grid, dim3(kThreads), kSmemTotal, static_cast<cudaStream_t>(stream), a, qmap, kmap, vmap);
+  return check_launch("prefill_tc_kernel");
+}
+
+}  // namespace
+
+// Reads and clears this file's share of the device error word (pkv_debug_device_flags).
+int prefill_read_flags(unsigned int* flags) {
+  unsigned int v = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_pkv_prefill_error, sizeof(v));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_pkv_prefill_error, &zero, sizeof(zero));
+  if (e != cudaSuccess) return fail(PKV_E_CUDA, "pkv_debug_device_flags: %s", cudaGetErrorString(e));
+  *flags = v;
+  return PKV_OK;
+}
+
+}  // namespace pkv
 
 extern "C" {
-int pkv_prefill_attn_bf16(const void*, const void*, const void*, const int*, const int*, const int*, const int*,
-                          const int*, void*, int, int, int, int, int, int, int, float, pkv_stream) {
-  return pkv::fail(PKV_E_UNSUPPORTED, "pkv_prefill_attn_bf16: kernel not built into this library");
+int pkv_prefill_attn_bf16(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                          const int* table_offset, const int* q_start, const int* q_len, const int* ctx_len,
+                          void* out, int n_tokens, int n_seqs, int max_q_len, int q_heads, int kv_heads,
+                          int head_dim, int block_size, int num_blocks, float scale, pkv_stream stream) {
+  return pkv::prefill_impl<__nv_bfloat16>(q, k_cache, v_cache, block_tables, table_offset, q_start, q_len, ctx_len, out,
+                                          n_tokens, n_seqs, max_q_len, q_heads, kv_heads, head_dim, block_size,
+                                          num_blocks, scale, stream);
 }
-int pkv_prefill_attn_f16(const void*, const void*, const void*, const int*, const int*, const int*, const int*,
-                         const int*, void*, int, int, int, int, int, int, int, float, pkv_stream) {
-  return pkv::fail(PKV_E_UNSUPPORTED, "pkv_prefill_attn_f16: kernel not built into this library");
+int pkv_prefill_attn_f16(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                         const int* table_offset, const int* q_start, const int* q_len, const int* ctx_len,
+                         void* out, int n_tokens, int n_seqs, int max_q_len, int q_heads, int kv_heads,
+                         int head_dim, int block_size, int num_blocks, float scale, pkv_stream stream) {
+  return pkv::prefill_impl<__half>(q, k_cache, v_cache, block_tables, table_offset, q_start, q_len, ctx_len, out,
+                                   n_tokens, n_seqs, max_q_len, q_heads, kv_heads, head_dim, block_size, num_blocks,
+                                   scale, stream);
 }
 }

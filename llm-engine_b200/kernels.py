@@ -120,12 +120,12 @@ class DecodePlan:
 
 
 def launch_attention_prefill(q, k_cache, v_cache, block_tables, table_offset, q_start, q_len, ctx_len, out,
-                             n_seqs: int, max_q_len: int, q_heads: int, kv_heads: int, head_dim: int,
+                             n_tokens: int, n_seqs: int, max_q_len: int, q_heads: int, kv_heads: int, head_dim: int,
                              block_size: int, num_blocks: int, scale: float, stream=None) -> None:
     """Causal attention of each sequence's new chunk over its cached plus new tokens."""
     fn = f"pkv_prefill_attn_{_suffix(k_cache)}"
     st = getattr(_lib.lib(), fn)(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(table_offset),
-                                 _ptr(q_start), _ptr(q_len), _ptr(ctx_len), _ptr(out), n_seqs, max_q_len, q_heads,
+                                 _ptr(q_start), _ptr(q_len), _ptr(ctx_len), _ptr(out), n_tokens, n_seqs, max_q_len, q_heads,
                                  kv_heads, head_dim, block_size, num_blocks, C.c_float(scale), _stream(stream))
     _lib.check(fn, st)
 
