@@ -43,17 +43,18 @@ WORKLOAD_TEXT = {
     "cfg1": "one Qwen2.5-0.5B attention layer (14q/2kv heads, d64), fp32 KV, 8 seqs, ctx U[64,512], block 16, 4096-block shuffled pool",
     "cfg2": "Qwen2.5-0.5B decode step: 24 layers, 14q/2kv heads, d64, bf16 KV, 64 seqs, ctx U[256,2048], block 16, shuffled pool",
     "cfg3": "TinyLlama-1.1B decode step: 22 layers, 32q/4kv heads, d64, bf16 KV, 256 seqs, ctx log-uniform [128,8192], block 16, fragmented 65536-block pool per layer",
+    "cfg4": "chunked prefill, Qwen2.5-0.5B attention shapes (14q/2kv heads, d64), bf16: 32 seqs, cached context U[0,1536] + 512-token chunk, causal over cached+new, block 16, shuffled tables; one step = append + prefill attention for 24 layers",
     "cfg5": "prefix-cache decode: TinyLlama shapes, 22 layers, 128 seqs sharing a 512-token prefix + suffix U[32,256], bf16 KV, block 16",
 }
 METRIC = "decode tok/s (K/V append + paged decode attention over all layers)"
 
 
-def peaks():
+def peaks(key="hbm_gbs", fallback=6650.0):
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         with open(p) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
-    return 6650.0, "fallback (earlier measurement on this pool)"
+            return float(json.load(f)[key]), "measured (MEASURED_PEAKS.json)"
+    return fallback, "fallback (earlier measurement on this pool)"
 
 
 class ClockSampler:
@@ -411,6 +412,148 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_prefill(args, rank, local_rank, world):
+    """--workload cfg4: chunked paged prefill.  One step = for every layer, append the chunk's K/V rows
+    and run the tcgen05 prefill attention kernel.  Metric: prompt tokens/s; roofline: tensor."""
+    import torch
+    import torch.distributed as dist
+
+    pkv = importlib.import_module("llm-engine_b200")
+    wl = importlib.import_module("llm-engine_b200.workloads")
+    sh = importlib.import_module("llm-engine_b200.sharding")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = args.layers or 24
+    w = wl.make("cfg4", seed=sh.rank_seed(1238, rank), layers=L)
+    tdt = torch.bfloat16
+    bs, kv_dim = w.block_size, w.kv_dim
+    H = w.q_heads * w.head_dim
+    tabs, pos, _ = w.step_tokens()
+    idx = pkv.pack_step(tabs, pos, bs)
+    N = idx.n_tokens
+    slots_total = w.num_blocks * bs
+    g = torch.Generator(device=dev).manual_seed(91 + rank)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(tdt)
+    pools = rnd(L, 2, slots_total, kv_dim)
+    q, k, v = rnd(L, N, H), rnd(L, N, kv_dim), rnd(L, N, kv_dim)
+    out = torch.zeros((L, N, H), dtype=tdt, device=dev)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+    d_slots, d_tab, d_off = i32(idx.slots), i32(idx.block_tables), i32(idx.table_offset)
+    q_len = w.new.astype(np.int32)
+    q_start = np.concatenate([[0], np.cumsum(q_len)[:-1]]).astype(np.int32)
+    d_qs, d_ql, d_ctx = i32(q_start), i32(q_len), i32(w.ctx.astype(np.int32))
+    maxq = int(q_len.max())
+
+    def attn(l, q_l, out_l):
+        pkv.launch_attention_prefill(q_l, pools[l, 0], pools[l, 1], d_tab, d_off, d_qs, d_ql, d_ctx, out_l, N,
+                                     w.n_seqs, maxq, w.q_heads, w.kv_heads, w.head_dim, bs, w.num_blocks, w.scale)
+
+    def step():
+        for l in range(L):
+            pkv.launch_store_kv(k[l], v[l], d_slots, pools[l, 0], pools[l, 1], N, kv_dim)
+            attn(l, q[l], out[l])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        _, ms = sh.reduce_step(0.0, a.elapsed_time(b), dist if world > 1 else None, dev)
+        return ms
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    ms_step = timed(step, args.steps, args.warmup) / args.steps
+    clocks = sampler.stop()
+    tokens_all, _ = sh.reduce_step(float(N), 0.0, dist if world > 1 else None, dev)
+    value = tokens_all / (ms_step * 1e-3)
+    # per-launch time of the prefill kernel
+    evs = []
+    for _ in range(max(1, args.steps // 2)):
+        for l in range(L):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            attn(l, q[l], out[l])
+            b.record()
+            evs.append((a, b))
+    torch.cuda.synchronize()
+    k_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+    flops = w.prefill_flops_per_layer()
+    peak, src = peaks("bf16_tflops", 1590.0)
+    sust, _ = peaks("bf16_tflops_sustained", 1400.0)
+    ach = flops / (k_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                "frac": ach / peak, "frac_of_sustained": ach / sust, "traffic": None, "peak_source": src,
+                "algorithmic_flops_per_launch": flops, "us_per_launch": k_ms * 1e3, "launches_timed": len(evs)}
+    # end to end: the chunk's q/k/v rows from pinned host memory, outputs back
+    e2e = None
+    if not args.no_e2e:
+        pin = lambda t: t.cpu().pin_memory()
+        h_q, h_k, h_v = pin(q), pin(k), pin(v)
+        h_out = torch.empty((L, N, H), dtype=tdt).pin_memory()
+        e_q, e_k, e_v, e_out = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(out)
+        h_slots = torch.from_numpy(idx.slots).pin_memory()
+
+        def step_e2e():
+            d_slots.copy_(h_slots, non_blocking=True)
+            for l in range(L):
+                e_q[l].copy_(h_q[l], non_blocking=True)
+                e_k[l].copy_(h_k[l], non_blocking=True)
+                e_v[l].copy_(h_v[l], non_blocking=True)
+                pkv.launch_store_kv(e_k[l], e_v[l], d_slots, pools[l, 0], pools[l, 1], N, kv_dim)
+                attn(l, e_q[l], e_out[l])
+                h_out[l].copy_(e_out[l], non_blocking=True)
+
+        ms_e = timed(step_e2e, args.steps, args.warmup) / args.steps
+        e2e = {"value": tokens_all / (ms_e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e,
+               "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in (h_q, h_k, h_v)) + h_slots.numel() * 4),
+               "d2h_bytes_per_step": int(h_out.numel() * h_out.element_size()),
+               "matches_resident_output": bool(torch.equal(e_out, out))}
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import oracle
+        checker = oracle.load_ref() or oracle.load_orc()
+        kind = "reference" if checker.kind == "reference" else "port"
+        threads = oracle.ref_default_thread_count()
+        # bounded sample: every 16th chunk token of every sequence, one layer, scaled
+        orc = oracle.load_orc()
+        rng = np.random.default_rng(0)
+        kc = orc.from_bf16_bits(orc.to_bf16_bits(rng.standard_normal((slots_total, kv_dim), dtype=np.float32)))
+        vc = orc.from_bf16_bits(orc.to_bf16_bits(rng.standard_normal((slots_total, kv_dim), dtype=np.float32)))
+        sample = np.arange(0, N, 16)
+        qs = orc.from_bf16_bits(orc.to_bf16_bits(rng.standard_normal((sample.size, H), dtype=np.float32)))
+        t0 = time.perf_counter()
+        checker.paged_attention(qs, kc, vc, idx.block_tables, idx.table_offset, idx.token_seq[sample],
+                                idx.token_pos[sample], w.q_heads, w.kv_heads, w.head_dim, bs, w.scale, threads=threads)
+        t = time.perf_counter() - t0
+        cpu = {"value": N / (t * 16 * L), "unit": "tok/s", "cores": threads, "kind": kind,
+               "sample": f"attention for every 16th chunk token of all {w.n_seqs} sequences, 1 of {L} layers, scaled x16 x{L}"}
+    if rank == 0:
+        line = {"metric": "chunked prefill tok/s (K/V append + paged prefill attention over all layers)", "value": value,
+                "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"cfg4: {WORKLOAD_TEXT['cfg4']}", "tokens_per_step_per_gpu": N, "layers": L,
+                           "l2": "24 distinct per-layer pools and q/k/v/out sets (2.4 GB per step), larger than the 126 MB L2",
+                           "launch": "eager launches"},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 2 * L * args.steps, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -433,7 +576,10 @@ def main():
     if world != args.gpus:
         if args.gpus > 1 and world == 1:
             raise SystemExit("--gpus N > 1 is launched with torch.distributed.run --nproc-per-node N")
-    run_ours(args, rank, local_rank, world)
+    if args.workload == "cfg4":
+        run_prefill(args, rank, local_rank, world)
+    else:
+        run_ours(args, rank, local_rank, world)
 
 
 if __name__ == "__main__":

@@ -4,27 +4,29 @@
 // llm-engine has no prefill kernel (src/kernels/attention_prefill.cu:1 is a stub):
 // every prompt token goes through the decode kernel and re-reads its whole history.
 // Here a thread block takes 128 consecutive tokens of one sequence's chunk for one
-// query head and walks the keys in tiles of 128, so S = Q K^T and O = P V are dense
-// 128 x 128 x 64 contractions issued as tcgen05.mma with the accumulators in tensor
+// query head and walks the keys in tiles of 64, so S = Q K^T and O = P V are dense
+// 128 x 64 x 64 contractions issued as tcgen05.mma with the accumulators in tensor
 // memory.  The result it must agree with is ref::paged_attention_head
 // (include/engine/ops.h:87-111) applied to every (token, head) of the chunk.
 //
 // Roles inside a block of 192 threads:
-//   warp 4 (one lane)   TMA producer: the Q tile once, then per key tile eight boxes of
-//                       16 slots x 128 bytes for K and eight for V, gathered through the
-//                       block table into a two-stage ring (128-byte swizzle, which is
+//   warp 4 (one lane)   TMA producer: the Q tile once, then per key tile four boxes of
+//                       16 slots x 128 bytes for K and four for V, gathered through the
+//                       block table into a three-stage ring (128-byte swizzle, which is
 //                       also the canonical shared-memory layout of the MMA operands).
 //   warp 5 (one lane)   MMA issuer: S[j] = Q K_j^T (4 MMAs of K=16) into one of two S
-//                       buffers in tensor memory, then O_j = P_j V_j (8 MMAs) into one of
+//                       buffers in tensor memory, then O_j = P_j V_j (4 MMAs) into one of
 //                       two O-tile buffers; tcgen05.commit signals the mbarriers.
-//   warps 0-3           softmax: thread r owns row r (tensor-memory lane r).  Two passes
-//                       over S with tcgen05.ld (row max, then exp2 / row sum / P written
-//                       to shared memory as bf16 in the operand layout), causal mask by
-//                       absolute position; the running output lives in registers and
+//   warps 0-3           softmax: thread r owns row r (tensor-memory lane r).  The 64 scores
+//                       of the row come to registers with tcgen05.ld (the S buffer is
+//                       released at once), then row max, exp2 / row sum, P written to
+//                       shared memory in the operand layout; causal mask by absolute
+//                       position, applied only on tiles that reach the diagonal; the running output lives in registers and
 //                       each O tile is folded in with the usual rescale, so tensor
 //                       memory is never read-modify-written.
 // S[j+1] is issued before P_j V_j, so the tensor core works on the next scores while
-// the softmax warps are busy with the current ones.
+// the softmax warps are busy with the current ones; shared and tensor memory are
+// sized so that two blocks share an SM and fill each other's bubbles.
 //
 // Every mbarrier wait is bounded: a wait that runs out sets bit 2 of the device error
 // word and the block carries on to its tear-down (tensor memory is always released).
@@ -42,17 +44,20 @@ __device__ unsigned int g_pkv_prefill_error = 0;
 namespace {
 
 constexpr int kQTile = 128;     // query rows per block
-constexpr int kKTile = 128;     // keys per tile
+constexpr int kKTile = 64;      // keys per tile
 constexpr int kHd = 64;         // head_dim this kernel is written for
 constexpr int kThreads = 192;
-constexpr int kTileBytes = 128 * 128;            // 128 rows x 128 bytes
+constexpr int kKVStages = 3;
 constexpr int kBox = 16 * 128;                   // one TMA box: 16 slots x 128 bytes
+constexpr int kQBytes = kQTile * 128;            // 128 rows x 128 bytes
+constexpr int kKBytes = kKTile * 128;            // one K (or V, or P) tile: 64 keys x 128 bytes / 128 rows x 64 keys
+constexpr int kPBytes = kQTile * kKTile * 2;     // 128 rows x 64 keys, 16-bit
 constexpr int kSmemQ = 0;
-constexpr int kSmemKV = kSmemQ + kTileBytes;     // 2 stages x (K, V)
-constexpr int kSmemP = kSmemKV + 4 * kTileBytes; // 2 buffers x 2 blocks of 64 keys
-constexpr int kSmemTotal = kSmemP + 4 * kTileBytes + 1024;
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0, kTmemO = 256;     // S0 @0, S1 @128, O0 @256, O1 @320
+constexpr int kSmemKV = kSmemQ + kQBytes;                    // kKVStages x (K, V)
+constexpr int kSmemP = kSmemKV + kKVStages * 2 * kKBytes;    // 2 buffers
+constexpr int kSmemTotal = kSmemP + 2 * kPBytes + 1024;      // 97 KB: two blocks per SM
+constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
+constexpr uint32_t kTmemS = 0, kTmemO = 128;                 // S0 @0, S1 @64, O0 @128, O1 @192
 
 struct PrefillArgs {
   const int* block_tables;
@@ -110,10 +115,16 @@ __host__ __device__ constexpr uint32_t instr_desc(bool bf16, int n, bool b_mn_ma
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void give_up() { atomicOr(&g_pkv_prefill_error, 4u); }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
     prefill_tc_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap qmap,
                       const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -122,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[15];
+  __shared__ __align__(8) unsigned long long bars[17];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,14 +142,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sP = base + kSmemP;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, S_EMPTY = 7, P_FULL = 9, PV_DONE = 11, O_EMPTY = 13 };
+  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 4, S_FULL = 7, S_EMPTY = 9, P_FULL = 11, PV_DONE = 13, O_EMPTY = 15 };
 
   // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
   if (threadIdx.x == 0) {
     mbar_init(BAR(Q_FULL), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kKVStages; ++i) {
       mbar_init(BAR(KV_FULL + i), 1);
       mbar_init(BAR(KV_EMPTY + i), 1);   // arrived by tcgen05.commit after P_j V_j
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(BAR(S_FULL + i), 1);     // tcgen05.commit after Q K_j^T
       mbar_init(BAR(S_EMPTY + i), 128);  // every softmax thread, after its last read of S
       mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P
@@ -188,29 +201,29 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ================================ TMA producer ================================
     const int* tbl = a.block_tables + __ldg(a.table_offset + seq);
     if (lane == 0) {
-      mbar_arrive_expect_tx(BAR(Q_FULL), kTileBytes);
+      mbar_arrive_expect_tx(BAR(Q_FULL), kQBytes);
       tma_load_2d(sQ, &qmap, head * kHd, row0, BAR(Q_FULL));
     }
     for (int j = 0; j < n_kt; ++j) {
-      const int st = j & 1;
-      const int rel = j * kKTile + (lane & 7) * 16;
+      const int st = j % kKVStages;
+      const int rel = j * kKTile + (lane & 3) * 16;
       int ent = 0;
       if (rel < kv_total) ent = __ldg(tbl + (rel >> a.bs_log2));
-      int y[8];
+      int y[4];
 #pragma unroll
-      for (int b = 0; b < 8; ++b) {
+      for (int b = 0; b < 4; ++b) {
         const int e = __shfl_sync(0xffffffffu, ent, b);
         y[b] = (e << a.bs_log2) + ((j * kKTile + 16 * b) & (a.block_size - 1));
       }
       if (lane == 0) {
-        WAIT(BAR(KV_EMPTY + st), ((j >> 1) & 1) ^ 1);
+        WAIT(BAR(KV_EMPTY + st), ((j / kKVStages) & 1) ^ 1);
         int nvalid = 0;
 #pragma unroll
-        for (int b = 0; b < 8; ++b) nvalid += (j * kKTile + 16 * b < kv_total) ? 1 : 0;
+        for (int b = 0; b < 4; ++b) nvalid += (j * kKTile + 16 * b < kv_total) ? 1 : 0;
         mbar_arrive_expect_tx(BAR(KV_FULL + st), static_cast<uint32_t>(nvalid) * 2u * kBox);
-        const uint32_t kdst = sKV + st * 2 * kTileBytes, vdst = kdst + kTileBytes;
+        const uint32_t kdst = sKV + st * 2 * kKBytes, vdst = kdst + kKBytes;
 #pragma unroll
-        for (int b = 0; b < 8; ++b) {
+        for (int b = 0; b < 4; ++b) {
           if (j * kKTile + 16 * b < kv_total) {
             tma_load_2d(kdst + b * kBox, &kmap, kvh * kHd, y[b], BAR(KV_FULL + st));
             tma_load_2d(vdst + b * kBox, &vmap, kvh * kHd, y[b], BAR(KV_FULL + st));
@@ -224,31 +237,30 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       WAIT(BAR(Q_FULL), 0);
       auto issue_qk = [&](int j) {
-        const int st = j & 1;
-        WAIT(BAR(KV_FULL + st), (j >> 1) & 1);
-        WAIT(BAR(S_EMPTY + st), ((j >> 1) & 1) ^ 1);
+        const int st = j % kKVStages, sb = j & 1;
+        WAIT(BAR(KV_FULL + st), (j / kKVStages) & 1);
+        WAIT(BAR(S_EMPTY + sb), ((j >> 1) & 1) ^ 1);
         tc_fence_after();
-        const uint32_t ks_base = sKV + st * 2 * kTileBytes;
+        const uint32_t k_base = sKV + st * 2 * kKBytes;
 #pragma unroll
         for (int ks = 0; ks < kHd / 16; ++ks)
-          tc_mma(tmem + kTmemS + st * 128, smem_desc(sQ + ks * 32), smem_desc(ks_base + ks * 32), kIdescQK, ks > 0);
-        tc_commit(BAR(S_FULL + st));
+          tc_mma(tmem + kTmemS + sb * 64, smem_desc(sQ + ks * 32), smem_desc(k_base + ks * 32), kIdescQK, ks > 0);
+        tc_commit(BAR(S_FULL + sb));
       };
       issue_qk(0);
       for (int j = 0; j < n_kt; ++j) {
-        const int st = j & 1;
+        const int st = j % kKVStages, sb = j & 1;
         if (j + 1 < n_kt) issue_qk(j + 1);
-        WAIT(BAR(P_FULL + st), (j >> 1) & 1);
-        WAIT(BAR(O_EMPTY + st), ((j >> 1) & 1) ^ 1);
+        WAIT(BAR(P_FULL + sb), (j >> 1) & 1);
+        WAIT(BAR(O_EMPTY + sb), ((j >> 1) & 1) ^ 1);
         tc_fence_after();
-        const uint32_t v_base = sKV + st * 2 * kTileBytes + kTileBytes;
-        const uint32_t p_base = sP + st * 2 * kTileBytes;
+        const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
+        const uint32_t p_base = sP + sb * kPBytes;
 #pragma unroll
         for (int kk = 0; kk < kKTile / 16; ++kk)
-          tc_mma(tmem + kTmemO + st * 64, smem_desc(p_base + (kk >> 2) * kTileBytes + (kk & 3) * 32),
-                 smem_desc(v_base + kk * 2048), kIdescPV, kk > 0);
+          tc_mma(tmem + kTmemO + sb * 64, smem_desc(p_base + kk * 32), smem_desc(v_base + kk * kBox), kIdescPV, kk > 0);
         tc_commit(BAR(KV_EMPTY + st));
-        tc_commit(BAR(PV_DONE + st));
+        tc_commit(BAR(PV_DONE + sb));
       }
     }
     __syncwarp();
@@ -261,97 +273,90 @@ __global__ void __launch_bounds__(kThreads, 1)
     float o[kHd];
 #pragma unroll
     for (int d = 0; d < kHd; ++d) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
 
-    auto fold_o_tile = [&](int jj) {   // o += O tile of key tile jj
-      const int st = jj & 1;
-      WAIT(BAR(PV_DONE + st), (jj >> 1) & 1);
+    // o = o * alpha + O tile jj, where alpha is the rescale decided when tile jj's scores were seen
+    auto fold_o_tile = [&](int jj, float alpha) {
+      const int sb = jj & 1;
+      WAIT(BAR(PV_DONE + sb), (jj >> 1) & 1);
       tc_fence_after();
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t v[32];
-        tc_ld32(tmem + lane_addr + kTmemO + st * 64 + h * 32, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[h * 32 + i] += __uint_as_float(v[i]);
-      }
+      uint32_t v0[32], v1[32];
+      tc_ld32(tmem + lane_addr + kTmemO + sb * 64, v0);
+      tc_ld32(tmem + lane_addr + kTmemO + sb * 64 + 32, v1);
+      tc_wait_ld();
       tc_fence_before();
-      mbar_arrive(BAR(O_EMPTY + st));
+      mbar_arrive(BAR(O_EMPTY + sb));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        o[i] = fmaf(o[i], alpha, __uint_as_float(v0[i]));
+        o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(v1[i]));
+      }
     };
 
     for (int j = 0; j < n_kt; ++j) {
-      const int st = j & 1;
+      const int sb = j & 1;
       const int k0 = j * kKTile;
-      WAIT(BAR(S_FULL + st), (j >> 1) & 1);
+      WAIT(BAR(S_FULL + sb), (j >> 1) & 1);
       tc_fence_after();
-      const bool masked = k0 + kKTile - 1 > limit;
-      // pass 1: row maximum (raw scores; the scale is positive, so it commutes with max)
-      float mx = -INFINITY;
-#pragma unroll
-      for (int cblk = 0; cblk < 4; ++cblk) {
-        uint32_t v[32];
-        tc_ld32(tmem + lane_addr + kTmemS + st * 128 + cblk * 32, v);
+      float sc[kKTile];
+      {
+        uint32_t v0[32], v1[32];
+        tc_ld32(tmem + lane_addr + kTmemS + sb * 64, v0);
+        tc_ld32(tmem + lane_addr + kTmemS + sb * 64 + 32, v1);
         tc_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (masked && k0 + cblk * 32 + i > limit) s = -INFINITY;
-          mx = fmaxf(mx, s);
-        }
-      }
-      const float m_new = fmaxf(m_run, mx);          // finite: key 0 is visible to every row
-      const float alpha = exp2f((m_run - m_new) * sl2);
-      const float neg = -m_new * sl2;
-      m_run = m_new;
-      // the P buffer is free once P_{j-2} V_{j-2} has completed
-      WAIT(BAR(PV_DONE + st), ((j >> 1) & 1) ^ 1);
-      // pass 2: p = exp2(s * scale * log2e - m), row sum, P to shared memory in operand layout
-      float psum = 0.f;
-      unsigned char* prow = base_ptr + kSmemP + st * 2 * kTileBytes + r * 128;
-#pragma unroll
-      for (int cblk = 0; cblk < 4; ++cblk) {
-        uint32_t v[32];
-        tc_ld32(tmem + lane_addr + kTmemS + st * 128 + cblk * 32, v);
-        tc_wait_ld();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-          if (masked && k0 + cblk * 32 + i > limit) s0 = -INFINITY;
-          if (masked && k0 + cblk * 32 + i + 1 > limit) s1 = -INFINITY;
-          const float p0 = exp2f(fmaf(s0, sl2, neg)), p1 = exp2f(fmaf(s1, sl2, neg));
-          psum += p0 + p1;
-          packed[i >> 1] = pack2<T>(p0, p1);
-        }
-        // 32 keys = 4 chunks of 16 bytes; keys 0-63 live in block 0 of the buffer, 64-127 in block 1
-        unsigned char* blk = prow + (cblk >> 1) * kTileBytes;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (cblk & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(blk + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          sc[i] = __uint_as_float(v0[i]);
+          sc[32 + i] = __uint_as_float(v1[i]);
         }
       }
       tc_fence_before();
-      mbar_arrive(BAR(S_EMPTY + st));                // S buffer may be overwritten by Q K_{j+2}^T
+      mbar_arrive(BAR(S_EMPTY + sb));                // the scores are in registers: S may be overwritten
+      // Causal mask, only on tiles that reach past some row's last visible key (warp-uniform test).
+      if (__any_sync(0xffffffffu, k0 + kKTile - 1 > limit)) {
+#pragma unroll
+        for (int i = 0; i < kKTile; ++i)
+          if (k0 + i > limit) sc[i] = -INFINITY;
+      }
+      float mx = sc[0];
+#pragma unroll
+      for (int i = 1; i < kKTile; ++i) mx = fmaxf(mx, sc[i]);
+      const float m_new = fmaxf(m_run, mx);          // finite: key 0 is visible to every row (raw scores; scale > 0)
+      const float alpha = ex2_approx((m_run - m_new) * sl2);
+      const float neg = -m_new * sl2;
+      m_run = m_new;
+      WAIT(BAR(PV_DONE + sb), ((j >> 1) & 1) ^ 1);   // P buffer free: P_{j-2} V_{j-2} has completed
+      float psum = 0.f;
+      unsigned char* prow = base_ptr + kSmemP + sb * kPBytes + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < kKTile / 8; ++ch) {
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          p[i] = ex2_approx(fmaf(sc[ch * 8 + i], sl2, neg));
+          psum += p[i];
+        }
+        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
+            make_uint4(pack2<T>(p[0], p[1]), pack2<T>(p[2], p[3]), pack2<T>(p[4], p[5]), pack2<T>(p[6], p[7]));
+      }
       l_run = l_run * alpha + psum;
       if (j == n_kt - 1 && kv_total - k0 < kKTile) {
         // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
         // behind them are whatever the pool or the ring held; clear them so 0 * x stays 0.
-        WAIT(BAR(KV_FULL + st), (j >> 1) & 1);
-        if (r >= kv_total - k0) {
-          unsigned char* vrow = base_ptr + kSmemKV + st * 2 * kTileBytes + kTileBytes + r * 128;
+        const int st = j % kKVStages;
+        WAIT(BAR(KV_FULL + st), (j / kKVStages) & 1);
+        if (r < kKTile && r >= kv_total - k0) {
+          unsigned char* vrow = base_ptr + kSmemKV + st * 2 * kKBytes + kKBytes + r * 128;
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vrow + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // P (and V) stores before the MMA reads them
-      mbar_arrive(BAR(P_FULL + st));
-      if (j > 0) fold_o_tile(j - 1);
-#pragma unroll
-      for (int d = 0; d < kHd; ++d) o[d] *= alpha;
+      mbar_arrive(BAR(P_FULL + sb));
+      if (j > 0) fold_o_tile(j - 1, alpha_prev);
+      alpha_prev = alpha;
     }
-    fold_o_tile(n_kt - 1);
+    fold_o_tile(n_kt - 1, alpha_prev);
     if (r < rows_here) {
       const float inv = 1.f / l_run;
       T* orow = static_cast<T*>(a.out) + (static_cast<size_t>(row0 + r) * a.q_heads + head) * kHd;
