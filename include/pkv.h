@@ -104,6 +104,30 @@ int pkv_decode_attn_f32(const void* q, const void* k_cache, const void* v_cache,
                         int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size,
                         float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
 
+/* The same operation for callers that cannot hand over a workspace because they cannot
+ * allocate one: code that runs where device allocation is off the table -- a serving
+ * engine that gave every free byte of HBM to its block pool at start-up (a later
+ * cudaMalloc fails or fragments), or a per-token loop where cudaMalloc's implicit
+ * device synchronisation is not acceptable.  Split-K scratch is a fixed 32 MiB area
+ * inside the library's device image (each GPU that loads the library holds it until
+ * the process exits); this call allocates nothing and calls no allocating routine.
+ * Limits and rules:
+ *   - a step whose plan does not fit the area returns PKV_E_WORKSPACE with the sizes
+ *     in pkv_last_error() (at head_dim 64: about 1,900 extra split items at 32 query
+ *     heads, 4,400 at 14); use pkv_decode_attn_bf16 with your own workspace then;
+ *   - the first call on each device looks the area's address up
+ *     (cudaGetSymbolAddress, with that device current): make that first call before
+ *     any stream capture begins;
+ *   - every call on a device shares the one area and rebuilds all of it that it reads
+ *     (the plan is rewritten at each call), so nothing needs clearing between calls,
+ *     but two calls that overlap on the GPU (different streams) race: serialise them.
+ * This entry point has no counterpart in llm-engine. */
+int pkv_decode_attn_bf16_builtin_scratch(const void* q, const void* k_cache, const void* v_cache,
+                                         const int* block_tables, const int* table_offset,
+                                         const int* token_seq, const int* token_pos, void* out,
+                                         int n_tokens, int q_heads, int kv_heads, int head_dim,
+                                         int block_size, float scale, pkv_stream stream);
+
 /* Plan-once form.  A decode step calls attention once per layer with the SAME
  * index arrays (src/model/cuda/cuda_model.cu:349-377), so the split-K work list
  * can be built once per step and reused by every layer.

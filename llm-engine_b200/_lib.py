@@ -38,6 +38,7 @@ SIGNATURES = {
     **{f"pkv_append_{s}": (_i, [_vp] * 5 + [_i, _i, _vp]) for s in ("f16", "bf16", "f32")},
     "pkv_decode_workspace_bytes": (_sz, [_i] * 4),
     **{f"pkv_decode_attn_{s}": (_i, [_vp] * 8 + [_i] * 5 + [_f, _vp, _sz, _vp]) for s in ("f16", "bf16", "f32")},
+    "pkv_decode_attn_bf16_builtin_scratch": (_i, [_vp] * 8 + [_i] * 5 + [_f, _vp]),
     "pkv_decode_plan_staging_bytes": (_sz, [_i, _i]),
     "pkv_decode_plan_host": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
     "pkv_decode_plan_device": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, C.POINTER(DecodePlan)]),

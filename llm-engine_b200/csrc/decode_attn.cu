@@ -4,12 +4,19 @@
 #include <cstdlib>
 #include <type_traits>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "decode_attn.cuh"
 #include "decode_tma.cuh"
 #include "launch_util.hpp"
 #include "status.hpp"
+
+// Scratch for pkv_decode_attn_bf16_builtin_scratch: lives in the library's own device
+// image, one copy per GPU that loads it, for the life of the process.  In host code
+// this name is only a handle for cudaGetSymbolAddress, never a usable pointer.
+constexpr size_t kBuiltinScratchBytes = 32u << 20;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
 
 namespace pkv {
 int prefill_read_flags(unsigned int* flags);  // prefill_attn.cu
@@ -539,6 +546,49 @@ int pkv_decode_plan_device(const int* token_pos, int n_tokens, int q_heads, int 
   if (st != PKV_OK) return st;
   return plan_device(token_pos, n_tokens, q_heads, kv_heads, head_dim, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream), plan);
+}
+
+// Device address of g_builtin_scratch on the current device, looked up once per device.
+static int builtin_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(PKV_E_CUDA, "pkv_decode_attn_bf16_builtin_scratch: no current device");
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_builtin_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(PKV_E_CUDA, "pkv_decode_attn_bf16_builtin_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return PKV_OK;
+}
+
+int pkv_decode_attn_bf16_builtin_scratch(const void* q, const void* k_cache, const void* v_cache,
+                                         const int* block_tables, const int* table_offset, const int* token_seq,
+                                         const int* token_pos, void* out, int n_tokens, int q_heads, int kv_heads,
+                                         int head_dim, int block_size, float scale, pkv_stream stream) {
+  const char* fn = "pkv_decode_attn_bf16_builtin_scratch";
+  if (n_tokens <= 0 || q_heads <= 0) return PKV_OK;
+  int st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, block_size);
+  if (st != PKV_OK) return st;
+  // The step's plan plus room for one GPU-wide wave of extra split-K items must fit.
+  const int min_extra = (tuning().wave_ctas / 3 + kv_heads - 1) / kv_heads;
+  const size_t need = ws_layout(n_tokens, q_heads, kv_heads, head_dim, min_extra).total;
+  if (need > kBuiltinScratchBytes)
+    return fail(PKV_E_WORKSPACE,
+                "%s: a step of %d tokens x %d heads x head_dim %d needs %zu bytes of scratch, the built-in area holds %zu; "
+                "use pkv_decode_attn_bf16 with a caller-owned workspace",
+                fn, n_tokens, q_heads, head_dim, need, kBuiltinScratchBytes);
+  void* ws = nullptr;
+  st = builtin_scratch_address(&ws);
+  if (st != PKV_OK) return st;
+  return decode_all_in_one<__nv_bfloat16>(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,
+                                          n_tokens, q_heads, kv_heads, head_dim, block_size, scale, ws,
+                                          kBuiltinScratchBytes, stream);
 }
 
 #define PKV_DECODE_ENTRY(SUFFIX, TYPE)                                                                               \
