@@ -206,7 +206,9 @@ def run_ours(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=dev)
 
     sh = importlib.import_module("llm-engine_b200.sharding")
-    w = wl.make(args.workload, seed=sh.rank_seed(1234 + int(args.workload[-1]), rank), layers=args.layers)
+    # Weak scaling: every rank gets the configuration's batch with the SAME lengths and table shapes
+    # (fixed work per GPU); only the tensor contents differ per rank (generator seeds below).
+    w = wl.make(args.workload, layers=args.layers)
     tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[w.dtype]
     bs, kv_dim, L = w.block_size, w.kv_dim, w.layers
     H = w.q_heads * w.head_dim
@@ -426,7 +428,7 @@ def run_prefill(args, rank, local_rank, world):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L = args.layers or 24
-    w = wl.make("cfg4", seed=sh.rank_seed(1238, rank), layers=L)
+    w = wl.make("cfg4", layers=L)
     tdt = torch.bfloat16
     bs, kv_dim = w.block_size, w.kv_dim
     H = w.q_heads * w.head_dim

@@ -15,15 +15,15 @@
 //                       block table into a three-stage ring (128-byte swizzle, which is
 //                       also the canonical shared-memory layout of the MMA operands).
 //   warp 5 (one lane)   MMA issuer: S[j] = Q K_j^T (4 MMAs of K=16) into one of two S
-//                       buffers in tensor memory, then O_j = P_j V_j (4 MMAs) into one of
-//                       two O-tile buffers; tcgen05.commit signals the mbarriers.
+//                       buffers in tensor memory, then O += P_j V_j (4 MMAs, plus 4 narrow
+//                       ones for the row sums); tcgen05.commit signals the mbarriers.
 //   warps 0-3           softmax: thread r owns row r (tensor-memory lane r).  The 64 scores
 //                       of the row come to registers with tcgen05.ld (the S buffer is
-//                       released at once), then row max, exp2 / row sum, P written to
-//                       shared memory in the operand layout; causal mask by absolute
-//                       position, applied only on tiles that reach the diagonal; the running output lives in registers and
-//                       each O tile is folded in with the usual rescale, so tensor
-//                       memory is never read-modify-written.
+//                       released at once), then row max, exp2, P written to shared memory
+//                       in the operand layout; causal mask by absolute position, applied
+//                       only on tiles that reach the diagonal.  O and the row sums (a
+//                       second MMA against a tile of ones) accumulate in tensor memory and
+//                       are rescaled only when a row's maximum has grown by more than 2^8.
 // S[j+1] is issued before P_j V_j, so the tensor core works on the next scores while
 // the softmax warps are busy with the current ones; shared and tensor memory are
 // sized so that two blocks share an SM and fill each other's bubbles.
@@ -55,9 +55,11 @@ constexpr int kPBytes = kQTile * kKTile * 2;     // 128 rows x 64 keys, 16-bit
 constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kSmemQ + kQBytes;                    // kKVStages x (K, V)
 constexpr int kSmemP = kSmemKV + kKVStages * 2 * kKBytes;    // 2 buffers
-constexpr int kSmemTotal = kSmemP + 2 * kPBytes + 1024;      // 97 KB: two blocks per SM
+constexpr int kSmemOnes = kSmemP + 2 * kPBytes;              // a V-shaped tile of 1.0: P x ones = row sums
+constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 105 KB: two blocks per SM
 constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
-constexpr uint32_t kTmemS = 0, kTmemO = 128;                 // S0 @0, S1 @64, O0 @128, O1 @192
+constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64), row sums @192 (16)
+constexpr float kRescaleThreshold = 8.f;                     // in log2 units: P stays below 2^8
 
 struct PrefillArgs {
   const int* block_tables;
@@ -94,6 +96,17 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes packed 8 to a
@@ -130,19 +143,20 @@ __global__ void __launch_bounds__(kThreads, 2)
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr uint32_t kIdescQK = instr_desc(kBf16, kKTile, false);
   constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd, true);
+  constexpr uint32_t kIdescL = instr_desc(kBf16, 16, true);
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[17];
+  __shared__ __align__(8) unsigned long long bars[15];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sP = base + kSmemP;
+  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sP = base + kSmemP, sOnes = base + kSmemOnes;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 4, S_FULL = 7, S_EMPTY = 9, P_FULL = 11, PV_DONE = 13, O_EMPTY = 15 };
+  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 4, S_FULL = 7, S_EMPTY = 9, P_FULL = 11, PV_DONE = 13 };
 
   // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
   if (threadIdx.x == 0) {
@@ -155,8 +169,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(BAR(S_FULL + i), 1);     // tcgen05.commit after Q K_j^T
       mbar_init(BAR(S_EMPTY + i), 128);  // every softmax thread, after its last read of S
       mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P
-      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O tile ready, P buffer free
-      mbar_init(BAR(O_EMPTY + i), 128);  // every softmax thread, after reading the O tile
+      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated, P buffer free
     }
     mbar_fence_init();
   }
@@ -252,13 +265,15 @@ __global__ void __launch_bounds__(kThreads, 2)
         const int st = j % kKVStages, sb = j & 1;
         if (j + 1 < n_kt) issue_qk(j + 1);
         WAIT(BAR(P_FULL + sb), (j >> 1) & 1);
-        WAIT(BAR(O_EMPTY + sb), ((j >> 1) & 1) ^ 1);
         tc_fence_after();
         const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
         const uint32_t p_base = sP + sb * kPBytes;
 #pragma unroll
-        for (int kk = 0; kk < kKTile / 16; ++kk)
-          tc_mma(tmem + kTmemO + sb * 64, smem_desc(p_base + kk * 32), smem_desc(v_base + kk * kBox), kIdescPV, kk > 0);
+        for (int kk = 0; kk < kKTile / 16; ++kk) {
+          // O += P_j V_j and, with a tile of ones in V's place, the row sums of P_j (16 equal columns)
+          tc_mma(tmem + kTmemO, smem_desc(p_base + kk * 32), smem_desc(v_base + kk * kBox), kIdescPV, (j | kk) != 0);
+          tc_mma(tmem + kTmemL, smem_desc(p_base + kk * 32), smem_desc(sOnes + kk * kBox), kIdescL, (j | kk) != 0);
+        }
         tc_commit(BAR(KV_EMPTY + st));
         tc_commit(BAR(PV_DONE + sb));
       }
@@ -270,28 +285,17 @@ __global__ void __launch_bounds__(kThreads, 2)
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const int limit = ctx + tile * kQTile + min(r, rows_here - 1);   // last visible key position of this row
     const float sl2 = a.scale * kLog2e;
-    float o[kHd];
+    // the tile of ones that turns the second MMA of every k-step into a row sum
+    if (r < kKTile) {
+      const uint32_t one2 = pack2<T>(1.f, 1.f);
+      unsigned char* orow = base_ptr + kSmemOnes + r * 128;
 #pragma unroll
-    for (int d = 0; d < kHd; ++d) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-
-    // o = o * alpha + O tile jj, where alpha is the rescale decided when tile jj's scores were seen
-    auto fold_o_tile = [&](int jj, float alpha) {
-      const int sb = jj & 1;
-      WAIT(BAR(PV_DONE + sb), (jj >> 1) & 1);
-      tc_fence_after();
-      uint32_t v0[32], v1[32];
-      tc_ld32(tmem + lane_addr + kTmemO + sb * 64, v0);
-      tc_ld32(tmem + lane_addr + kTmemO + sb * 64 + 32, v1);
-      tc_wait_ld();
-      tc_fence_before();
-      mbar_arrive(BAR(O_EMPTY + sb));
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        o[i] = fmaf(o[i], alpha, __uint_as_float(v0[i]));
-        o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(v1[i]));
-      }
-    };
+      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(orow + ch * 16) = make_uint4(one2, one2, one2, one2);
+    }
+    // Reference maximum of the row.  It follows the true running maximum lazily: O and the row
+    // sum stay in tensor memory and are only rescaled when the maximum has grown by more than
+    // 2^8, so most tiles cost no read-modify-write of the accumulator at all.
+    float m_used = -INFINITY;
 
     for (int j = 0; j < n_kt; ++j) {
       const int sb = j & 1;
@@ -321,25 +325,40 @@ __global__ void __launch_bounds__(kThreads, 2)
       float mx = sc[0];
 #pragma unroll
       for (int i = 1; i < kKTile; ++i) mx = fmaxf(mx, sc[i]);
-      const float m_new = fmaxf(m_run, mx);          // finite: key 0 is visible to every row (raw scores; scale > 0)
-      const float alpha = ex2_approx((m_run - m_new) * sl2);
-      const float neg = -m_new * sl2;
-      m_run = m_new;
+      if (j == 0) {
+        m_used = mx;                                 // finite: key 0 is visible to every row
+      } else if (__any_sync(0xffffffffu, (mx - m_used) * sl2 > kRescaleThreshold)) {
+        // Rare: bring this warp's rows of O and of the row sums to the new maximum.  Each thread
+        // owns its own tensor-memory lane; P_{j-1} V_{j-1} must have landed and P_j V_j cannot start
+        // before this thread has arrived on P_FULL below.
+        WAIT(BAR(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1);
+        tc_fence_after();
+        const float m_new = fmaxf(m_used, mx);
+        const float f = ex2_approx((m_used - m_new) * sl2);
+        m_used = m_new;
+#pragma unroll
+        for (int blk = 0; blk < 3; ++blk) {          // O: columns 128..191, row sums: 192..223
+          uint32_t v[32];
+          tc_ld32(tmem + lane_addr + kTmemO + blk * 32, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tc_st32(tmem + lane_addr + kTmemO + blk * 32, v);
+        }
+        tc_wait_st();
+        tc_fence_before();
+      }
+      const float neg = -m_used * sl2;
       WAIT(BAR(PV_DONE + sb), ((j >> 1) & 1) ^ 1);   // P buffer free: P_{j-2} V_{j-2} has completed
-      float psum = 0.f;
       unsigned char* prow = base_ptr + kSmemP + sb * kPBytes + r * 128;
 #pragma unroll
       for (int ch = 0; ch < kKTile / 8; ++ch) {
         float p[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          p[i] = ex2_approx(fmaf(sc[ch * 8 + i], sl2, neg));
-          psum += p[i];
-        }
+        for (int i = 0; i < 8; ++i) p[i] = ex2_approx(fmaf(sc[ch * 8 + i], sl2, neg));
         *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
             make_uint4(pack2<T>(p[0], p[1]), pack2<T>(p[2], p[3]), pack2<T>(p[4], p[5]), pack2<T>(p[6], p[7]));
       }
-      l_run = l_run * alpha + psum;
       if (j == n_kt - 1 && kv_total - k0 < kKTile) {
         // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
         // behind them are whatever the pool or the ring held; clear them so 0 * x stays 0.
@@ -351,23 +370,35 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vrow + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // P (and V) stores before the MMA reads them
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // P (ones, V) stores before the MMA reads them
       mbar_arrive(BAR(P_FULL + sb));
-      if (j > 0) fold_o_tile(j - 1, alpha_prev);
-      alpha_prev = alpha;
     }
-    fold_o_tile(n_kt - 1, alpha_prev);
-    if (r < rows_here) {
-      const float inv = 1.f / l_run;
-      T* orow = static_cast<T*>(a.out) + (static_cast<size_t>(row0 + r) * a.q_heads + head) * kHd;
+    // epilogue: O / row sum
+    WAIT(BAR(PV_DONE + ((n_kt - 1) & 1)), ((n_kt - 1) >> 1) & 1);
+    tc_fence_after();
+    {
+      uint32_t o0[32], o1[32], lv[32];
+      tc_ld32(tmem + lane_addr + kTmemO, o0);
+      tc_ld32(tmem + lane_addr + kTmemO + 32, o1);
+      tc_ld32(tmem + lane_addr + kTmemL, lv);
+      tc_wait_ld();
+      if (r < rows_here) {
+        const float inv = 1.f / __uint_as_float(lv[0]);
+        T* orow = static_cast<T*>(a.out) + (static_cast<size_t>(row0 + r) * a.q_heads + head) * kHd;
 #pragma unroll
-      for (int d = 0; d < kHd; d += 8) {
-        uint4 w;
-        w.x = pack2<T>(o[d] * inv, o[d + 1] * inv);
-        w.y = pack2<T>(o[d + 2] * inv, o[d + 3] * inv);
-        w.z = pack2<T>(o[d + 4] * inv, o[d + 5] * inv);
-        w.w = pack2<T>(o[d + 6] * inv, o[d + 7] * inv);
-        *reinterpret_cast<uint4*>(orow + d) = w;
+        for (int d = 0; d < 32; d += 8) {
+          uint4 w0, w1;
+          w0.x = pack2<T>(__uint_as_float(o0[d]) * inv, __uint_as_float(o0[d + 1]) * inv);
+          w0.y = pack2<T>(__uint_as_float(o0[d + 2]) * inv, __uint_as_float(o0[d + 3]) * inv);
+          w0.z = pack2<T>(__uint_as_float(o0[d + 4]) * inv, __uint_as_float(o0[d + 5]) * inv);
+          w0.w = pack2<T>(__uint_as_float(o0[d + 6]) * inv, __uint_as_float(o0[d + 7]) * inv);
+          w1.x = pack2<T>(__uint_as_float(o1[d]) * inv, __uint_as_float(o1[d + 1]) * inv);
+          w1.y = pack2<T>(__uint_as_float(o1[d + 2]) * inv, __uint_as_float(o1[d + 3]) * inv);
+          w1.z = pack2<T>(__uint_as_float(o1[d + 4]) * inv, __uint_as_float(o1[d + 5]) * inv);
+          w1.w = pack2<T>(__uint_as_float(o1[d + 6]) * inv, __uint_as_float(o1[d + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + d) = w0;
+          *reinterpret_cast<uint4*>(orow + 32 + d) = w1;
+        }
       }
     }
   }

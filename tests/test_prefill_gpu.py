@@ -104,10 +104,13 @@ def test_cfg4_chunked_prefill_sampled_at_full_size(pkv, orc, torch_cuda, workloa
                                case.bs, case.scale, threads=8)
     e_ref, e_row = rel_errors(got[sample].reshape(-1, 64), want.reshape(-1, 64))
     assert e_ref <= TOL["bf16"] and e_row <= TOL["bf16"], (e_ref, e_row)
-    # causality: poison the K/V rows of the last 100 chunk tokens of every sequence, rerun without the append
+    # causality: poison the K/V rows of the last 128 chunk tokens of every sequence (one whole query tile, so
+    # that no earlier token shares a thread block with a poisoned one), rerun without the append: every
+    # earlier token must come out bit-identical
     out_before = d["out"].clone()
-    later = np.concatenate([np.arange(s + n - 100, s + n) for s, n in zip(starts, new)])
+    later = np.concatenate([np.arange(s + n - 128, s + n) for s, n in zip(starts, new)])
     slots = torch.from_numpy(case.idx.slots[later].astype(np.int64)).cuda()
+    kc_saved, vc_saved = d["kc"].clone(), d["vc"].clone()
     d["kc"][slots] = 7.0
     d["vc"][slots] = -3.0
     i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).cuda()
@@ -117,3 +120,19 @@ def test_cfg4_chunked_prefill_sampled_at_full_size(pkv, orc, torch_cuda, workloa
     torch.cuda.synchronize()
     earlier = torch.from_numpy(np.setdiff1d(np.arange(case.N), later)).cuda()
     assert torch.equal(d["out"][earlier], out_before[earlier])
+    # ... and within a tile too: poison positions 450.. of every chunk; tokens 384..449 share a block with
+    # poisoned tokens (the lazy rescale may pick other reference maxima there), so they are compared by value
+    later2 = np.concatenate([np.arange(s + 450, s + n) for s, n in zip(starts, new)])
+    slots2 = torch.from_numpy(case.idx.slots[later2].astype(np.int64)).cuda()
+    d["kc"].copy_(kc_saved)
+    d["vc"].copy_(vc_saved)
+    d["kc"][slots2] = 9.0
+    d["vc"][slots2] = 5.0
+    pkv.launch_attention_prefill(d["q"], d["kc"], d["vc"], d["block_tables"], d["table_offset"], i32(starts),
+                                 i32(new), i32(ctx), d["out"], case.N, len(new), 512, case.qh, case.kvh, case.hd,
+                                 case.bs, case.nb, case.scale)
+    torch.cuda.synchronize()
+    mid = torch.from_numpy(np.concatenate([np.arange(s + 384, s + 450) for s in starts])).cuda()
+    a = d["out"][mid].float().cpu().numpy().reshape(-1, 64)
+    b = out_before[mid].float().cpu().numpy().reshape(-1, 64)
+    assert rel_errors(a, b)[1] <= 2e-2
