@@ -46,6 +46,11 @@ WORKLOAD_TEXT = {
     "cfg4": "chunked prefill, Qwen2.5-0.5B attention shapes (14q/2kv heads, d64), bf16: 32 seqs, cached context U[0,1536] + 512-token chunk, causal over cached+new, block 16, shuffled tables; one step = append + prefill attention for 24 layers",
     "cfg5": "prefix-cache decode: TinyLlama shapes, 22 layers, 128 seqs sharing a 512-token prefix + suffix U[32,256], bf16 KV, block 16",
 }
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the decode attention kernel, from the
+# ncu captures summarised under profiles/ (same per-launch workload as the default seed of each configuration).
+NCU_TRAFFIC = {
+    "cfg3": {"bytes": 429279488, "source": "profiles/decode_tma_kernel_cfg3_ncu_full.md (421.21 MB read + 8.07 MB written)"},
+}
 METRIC = "decode tok/s (K/V append + paged decode attention over all layers)"
 
 
@@ -367,7 +372,9 @@ def run_ours(args, rank, local_rank, world):
     achieved = algo_bytes / (attn_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": ("decode_tma_kernel + decode_combine_kernel" if w.dtype != "f32" else "decode_simt_kernel + decode_combine_kernel"),
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": algo_bytes,
+                "traffic": NCU_TRAFFIC.get(args.workload, {}).get("bytes"),
+                "traffic_source": NCU_TRAFFIC.get(args.workload, {}).get("source"),
+                "peak_source": peak_src, "algorithmic_bytes_per_launch": algo_bytes,
                 "us_per_launch": attn_ms * 1e3, "launches_timed": len(evs),
                 "frac_of_nominal_8TBs": achieved / 8000.0}
 

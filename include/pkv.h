@@ -76,6 +76,29 @@ int pkv_append_bf16(const void* k, const void* v, const int* slots, void* k_cach
 int pkv_append_f32(const void* k, const void* v, const int* slots, void* k_cache, void* v_cache,
                    int n_tokens, int kv_dim, pkv_stream stream);
 
+/* ------------------------------------------------------------------ f1 ----
+ * RoPE fused into the append.  Replaces the three launches llm-engine makes per layer,
+ * launch_rope(q), launch_rope(k), launch_store_kv (src/model/cuda/cuda_model.cu:366-368,
+ * src/kernels/rope.cu:32-62; arithmetic of ref::rope_inplace, include/engine/ops.h:56-68):
+ *   q[t][h][:]  <- rope(q[t][h][:], positions[t])            for the q_heads heads, in place
+ *   k_cache[slots[t]][h][:] <- rope(k[t][h][:], positions[t]) for the kv_heads heads
+ *   v_cache[slots[t]][:]    <- v[t][:]
+ * with x'[i] = x[i]*cos - x[i+D/2]*sin, x'[i+D/2] = x[i+D/2]*cos + x[i]*sin (rotate_half
+ * pairing), cos/sin = fp32 tables [max_positions][D/2] as built by ref::RopeTables
+ * (include/engine/ops.h:34-51).  Products are rounded separately (no fused multiply-add),
+ * so fp32 results equal the CPU code's bit for bit and 16-bit results equal its fp32 result
+ * rounded once.  Unlike the reference, `k` itself is left unrotated (nothing reads it
+ * after the append, src/model/cuda/cuda_model.cu:368-377).  head_dim must be even. */
+int pkv_rope_append_f16(void* q, const void* k, const void* v, const int* positions, const float* cos_table,
+                        const float* sin_table, const int* slots, void* k_cache, void* v_cache, int n_tokens,
+                        int q_heads, int kv_heads, int head_dim, pkv_stream stream);
+int pkv_rope_append_bf16(void* q, const void* k, const void* v, const int* positions, const float* cos_table,
+                         const float* sin_table, const int* slots, void* k_cache, void* v_cache, int n_tokens,
+                         int q_heads, int kv_heads, int head_dim, pkv_stream stream);
+int pkv_rope_append_f32(void* q, const void* k, const void* v, const int* positions, const float* cos_table,
+                        const float* sin_table, const int* slots, void* k_cache, void* v_cache, int n_tokens,
+                        int q_heads, int kv_heads, int head_dim, pkv_stream stream);
+
 /* ------------------------------------------------------------------ a2 ----
  * Paged decode attention.  Replaces engine::launch_attention_decode and
  * engine::launch_attention_decode_gqa (include/engine/cuda_kernels.h:48-62,

@@ -36,6 +36,7 @@ SIGNATURES = {
     "pkv_last_error": (C.c_char_p, []),
     "pkv_debug_device_flags": (_i, [_vp]),
     **{f"pkv_append_{s}": (_i, [_vp] * 5 + [_i, _i, _vp]) for s in ("f16", "bf16", "f32")},
+    **{f"pkv_rope_append_{s}": (_i, [_vp] * 9 + [_i] * 4 + [_vp]) for s in ("f16", "bf16", "f32")},
     "pkv_decode_workspace_bytes": (_sz, [_i] * 4),
     **{f"pkv_decode_attn_{s}": (_i, [_vp] * 8 + [_i] * 5 + [_f, _vp, _sz, _vp]) for s in ("f16", "bf16", "f32")},
     "pkv_decode_attn_bf16_builtin_scratch": (_i, [_vp] * 8 + [_i] * 5 + [_f, _vp]),

@@ -21,6 +21,7 @@ SOURCES = [
     "kv_cache_manager.cpp",
     "append.cu",
     "copy_blocks.cu",
+    "rope_append.cu",
     "decode_attn.cu",
     "prefill_attn.cu",
     "engine_shim.cu",

@@ -47,6 +47,17 @@ def launch_store_kv(k, v, slots, k_cache, v_cache, n_tokens: int, kv_dim: int, s
     _lib.check(fn, st)
 
 
+def launch_rope_store_kv(q, k, v, positions, cos_table, sin_table, slots, k_cache, v_cache, n_tokens: int,
+                         q_heads: int, kv_heads: int, head_dim: int, stream=None) -> None:
+    """launch_rope(q) + launch_rope(k) + launch_store_kv in one pass: q rotated in place, rotated k and v
+    written to their slots (cos/sin: fp32 tables [max_positions][head_dim/2])."""
+    fn = f"pkv_rope_append_{_suffix(k_cache)}"
+    st = getattr(_lib.lib(), fn)(_ptr(q), _ptr(k), _ptr(v), _ptr(positions), _ptr(cos_table), _ptr(sin_table),
+                                 _ptr(slots), _ptr(k_cache), _ptr(v_cache), n_tokens, q_heads, kv_heads, head_dim,
+                                 _stream(stream))
+    _lib.check(fn, st)
+
+
 def decode_workspace_bytes(n_tokens: int, q_heads: int, kv_heads: int, head_dim: int) -> int:
     return int(_lib.lib().pkv_decode_workspace_bytes(n_tokens, q_heads, kv_heads, head_dim))
 

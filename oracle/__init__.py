@@ -71,8 +71,29 @@ class Checker:
         f("paged_attention").restype = None
         f("paged_attention").argtypes = [C.c_void_p] * 8 + [C.c_int] * 5 + [C.c_float, C.c_int]
 
+        f("rope_tables").restype = None
+        f("rope_tables").argtypes = [C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
+        f("rope_inplace").restype = None
+        f("rope_inplace").argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+
     def _f(self, name):
         return getattr(self.lib, self.prefix + name)
+
+    # ---- rope --------------------------------------------------------------
+    def rope_tables(self, head_dim: int, max_positions: int, theta: float):
+        half = head_dim // 2
+        cos = np.zeros((max_positions, half), dtype=np.float32)
+        sin = np.zeros((max_positions, half), dtype=np.float32)
+        self._f("rope_tables")(head_dim, max_positions, C.c_float(theta), _ptr(cos), _ptr(sin))
+        return cos, sin
+
+    def rope(self, x: np.ndarray, heads: int, head_dim: int, positions, cos, sin) -> np.ndarray:
+        """x[n_tokens, heads*head_dim] fp32 -> rotated copy, token t at positions[t]."""
+        out = np.ascontiguousarray(x, dtype=np.float32).copy()
+        for t in range(out.shape[0]):
+            row = out[t]
+            self._f("rope_inplace")(row.ctypes.data_as(C.c_void_p), heads, head_dim, int(positions[t]), _ptr(cos), _ptr(sin))
+        return out
 
     # ---- scalar casts ------------------------------------------------------
     def f32_to_bf16(self, x: float) -> int:

@@ -161,6 +161,36 @@ int orc_step_pack(int n_tokens, const uint64_t* tok_seq_key, const int32_t* cons
   return n_seen;
 }
 
+/* -------------------------------------------------------------- rope ---- */
+
+/* include/engine/ops.h:34-51 : cos/sin tables [max_positions][head_dim/2], angles in double. */
+void orc_rope_tables(int head_dim, int max_positions, float theta, float* cos_out, float* sin_out) {
+  const int half = head_dim / 2;
+  for (int i = 0; i < half; i++) {
+    const double inv_freq = 1.0 / pow((double)theta, (2.0 * i) / head_dim);
+    for (int p = 0; p < max_positions; p++) {
+      const double angle = p * inv_freq;
+      cos_out[(size_t)p * half + i] = (float)cos(angle);
+      sin_out[(size_t)p * half + i] = (float)sin(angle);
+    }
+  }
+}
+
+/* include/engine/ops.h:56-68 : rotate_half RoPE in place on `heads` consecutive heads of one token. */
+void orc_rope_inplace(float* x, int heads, int head_dim, int pos, const float* cos_table, const float* sin_table) {
+  const int half = head_dim / 2;
+  const float* c = cos_table + (size_t)pos * half;
+  const float* s = sin_table + (size_t)pos * half;
+  for (int h = 0; h < heads; h++) {
+    float* v = x + h * head_dim;
+    for (int i = 0; i < half; i++) {
+      const float a = v[i], b = v[i + half];
+      v[i] = a * c[i] - b * s[i];
+      v[i + half] = b * c[i] + a * s[i];
+    }
+  }
+}
+
 /* ------------------------------------------------------------ append ---- */
 
 /* src/model/cpu/cpu_model.cpp:153-157 (CPU) and src/kernels/store_kv.cu:20-29

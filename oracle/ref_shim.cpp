@@ -111,6 +111,22 @@ void ref_bt_hashes(void* b, uint64_t* out) {
 }
 int64_t ref_bt_slot(void* b, int pos, int block_size) { return static_cast<BlockTable*>(b)->slot(pos, block_size); }
 
+// ---- RoPE (include/engine/ops.h:34-68) ------------------------------------
+void ref_rope_tables(int head_dim, int max_positions, float theta, float* cos_out, float* sin_out) {
+  engine::ref::RopeTables t;
+  t.build(head_dim, max_positions, theta);
+  std::memcpy(cos_out, t.cos.data(), t.cos.size() * sizeof(float));
+  std::memcpy(sin_out, t.sin.data(), t.sin.size() * sizeof(float));
+}
+void ref_rope_inplace(float* x, int heads, int head_dim, int pos, const float* cos_table, const float* sin_table) {
+  engine::ref::RopeTables t;
+  t.half = head_dim / 2;
+  const size_t n = static_cast<size_t>(pos + 1) * t.half;
+  t.cos.assign(cos_table, cos_table + n);
+  t.sin.assign(sin_table, sin_table + n);
+  engine::ref::rope_inplace(x, heads, head_dim, pos, t);
+}
+
 // ---- the hot path on host fp32 arrays --------------------------------------
 // K/V append: the reference does this inline with two memcpy calls per token
 // (src/model/cpu/cpu_model.cpp:153-157); there is no function to call, so the

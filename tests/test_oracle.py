@@ -209,3 +209,24 @@ def test_python_allocator_equals_compiled_reference_on_random_traces(ref):
     from oracle import kv_oracle
     from tests.test_kv_cache import random_trace_compare
     random_trace_compare(lambda nb, bs, p: oracle.ref_allocator(nb, bs, p), kv_oracle.Allocator, seeds=range(6))
+
+
+def test_rope_restatement_equals_compiled_reference(orc, ref):
+    """RoPE tables (include/engine/ops.h:34-51) and rotate_half rotation (ops.h:56-68), bit for bit."""
+    if ref is None:
+        pytest.skip("oracle/_ref/libpkv_ref.so not built (reference tree absent)")
+    for hd, theta in ((64, 10000.0), (128, 1000000.0), (6, 500.0)):
+        ca, sa = orc.rope_tables(hd, 300, theta)
+        cb, sb = ref.rope_tables(hd, 300, theta)
+        assert np.array_equal(ca.view(np.uint32), cb.view(np.uint32)) and np.array_equal(sa.view(np.uint32), sb.view(np.uint32))
+        x = np.random.default_rng(hd).standard_normal((7, 3 * hd)).astype(np.float32)
+        pos = [0, 1, 17, 299, 128, 64, 5]
+        a, b = orc.rope(x, 3, hd, pos, ca, sa), ref.rope(x, 3, hd, pos, cb, sb)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # known answers: position 0 is the identity; a quarter turn swaps the halves with a sign
+    c, s = orc.rope_tables(4, 2, 10000.0)
+    assert np.array_equal(c[0], np.ones(2, np.float32)) and np.array_equal(s[0], np.zeros(2, np.float32))
+    x = np.asarray([[1.0, 2.0, 3.0, 4.0]], dtype=np.float32)
+    assert np.array_equal(orc.rope(x, 1, 4, [0], c, s), x)
+    c90, s90 = np.zeros((1, 2), np.float32), np.ones((1, 2), np.float32)
+    assert orc.rope(x, 1, 4, [0], c90, s90).tolist() == [[-3.0, -4.0, 1.0, 2.0]]
