@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libpkv.so")
+LIB_PATH = os.environ.get("PKV_LIB_PATH") or os.path.join(_HERE, "libpkv.so")  # override: developer builds
 
 PKV_OK = 0
 PKV_E_ARG, PKV_E_UNSUPPORTED, PKV_E_WORKSPACE, PKV_E_CUDA, PKV_E_NOMEM, PKV_E_STATE = -1, -2, -3, -4, -5, -6

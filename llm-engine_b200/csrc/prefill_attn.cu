@@ -58,7 +58,7 @@ constexpr int kSmemP = kSmemKV + kKVStages * 2 * kKBytes;    // 2 buffers
 constexpr int kSmemOnes = kSmemP + 2 * kPBytes;              // a V-shaped tile of 1.0: P x ones = row sums
 constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 105 KB: two blocks per SM
 constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
-constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64), row sums @192 (16)
+constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64) with the row sums right behind (16)
 constexpr float kRescaleThreshold = 8.f;                     // in log2 units: P stays below 2^8
 
 struct PrefillArgs {
@@ -112,10 +112,12 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 // Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes packed 8 to a
 // 1024-byte group (stride-dimension offset 1024): the layout TMA writes and the
 // canonical layout of both K-major operands (Q, K, P) and the MN-major one (V).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+// `lbo_bytes` is the distance between successive 64-element column blocks of an MN-major
+// operand (unused for the K-major operands, whose K extent per MMA stays inside one row).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes = 16) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);
-  d |= static_cast<uint64_t>(1u) << 16;             // leading-dimension offset (unused with this swizzle)
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>(1024u >> 4) << 32;     // stride-dimension offset: next group of 8 rows
   d |= static_cast<uint64_t>(1u) << 46;             // descriptor version of this architecture
   d |= static_cast<uint64_t>(2u) << 61;             // SWIZZLE_128B
@@ -142,12 +144,11 @@ __global__ void __launch_bounds__(kThreads, 2)
                       const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr uint32_t kIdescQK = instr_desc(kBf16, kKTile, false);
-  constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd, true);
-  constexpr uint32_t kIdescL = instr_desc(kBf16, 16, true);
+  constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd + 16, true);   // 64 output dims + 16 row-sum columns
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[15];
+  __shared__ __align__(8) unsigned long long bars[13];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sP = base + kSmemP, sOnes = base + kSmemOnes;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 4, S_FULL = 7, S_EMPTY = 9, P_FULL = 11, PV_DONE = 13 };
+  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 4, S_FULL = 7, P_FULL = 9, PV_DONE = 11 };
 
   // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
   if (threadIdx.x == 0) {
@@ -167,7 +168,6 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(BAR(S_FULL + i), 1);     // tcgen05.commit after Q K_j^T
-      mbar_init(BAR(S_EMPTY + i), 128);  // every softmax thread, after its last read of S
       mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P
       mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated, P buffer free
     }
@@ -247,12 +247,19 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   } else if (warp == 5) {
     // ================================ MMA issuer ================================
+    // One thread issues everything, and every mbarrier wait and every tcgen05 instruction it
+    // executes costs it a few hundred cycles, so the schedule is kept to two waits, eight MMAs
+    // and three commits per key tile:
+    //  * no separate "S buffer free" barrier: a softmax thread reads S_{j-1} before it arrives on
+    //    P_FULL_{j-1}, which this thread has waited for before it overwrites that buffer with S_{j+1};
+    //  * O += P V and the row sums of P come out of ONE MMA of N = 80: the B operand is MN-major,
+    //    its first 64 columns are the V tile and its next column block, one leading-dimension
+    //    offset away, is a tile of ones.
     if (lane == 0) {
       WAIT(BAR(Q_FULL), 0);
       auto issue_qk = [&](int j) {
         const int st = j % kKVStages, sb = j & 1;
         WAIT(BAR(KV_FULL + st), (j / kKVStages) & 1);
-        WAIT(BAR(S_EMPTY + sb), ((j >> 1) & 1) ^ 1);
         tc_fence_after();
         const uint32_t k_base = sKV + st * 2 * kKBytes;
 #pragma unroll
@@ -269,11 +276,9 @@ __global__ void __launch_bounds__(kThreads, 2)
         const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
         const uint32_t p_base = sP + sb * kPBytes;
 #pragma unroll
-        for (int kk = 0; kk < kKTile / 16; ++kk) {
-          // O += P_j V_j and, with a tile of ones in V's place, the row sums of P_j (16 equal columns)
-          tc_mma(tmem + kTmemO, smem_desc(p_base + kk * 32), smem_desc(v_base + kk * kBox), kIdescPV, (j | kk) != 0);
-          tc_mma(tmem + kTmemL, smem_desc(p_base + kk * 32), smem_desc(sOnes + kk * kBox), kIdescL, (j | kk) != 0);
-        }
+        for (int kk = 0; kk < kKTile / 16; ++kk)
+          tc_mma(tmem + kTmemO, smem_desc(p_base + kk * 32), smem_desc(v_base + kk * kBox, sOnes - v_base), kIdescPV,
+                 (j | kk) != 0);
         tc_commit(BAR(KV_EMPTY + st));
         tc_commit(BAR(PV_DONE + sb));
       }
@@ -314,8 +319,8 @@ __global__ void __launch_bounds__(kThreads, 2)
           sc[32 + i] = __uint_as_float(v1[i]);
         }
       }
-      tc_fence_before();
-      mbar_arrive(BAR(S_EMPTY + sb));                // the scores are in registers: S may be overwritten
+      tc_fence_before();                             // the scores are in registers; arriving on P_FULL below
+                                                     // also tells the MMA thread that S may be overwritten
       // Causal mask, only on tiles that reach past some row's last visible key (warp-uniform test).
       if (__any_sync(0xffffffffu, k0 + kKTile - 1 > limit)) {
 #pragma unroll
