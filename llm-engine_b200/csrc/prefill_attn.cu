@@ -256,15 +256,17 @@ __global__ void __launch_bounds__(kThreads, 2)
     //    its first 64 columns are the V tile and its next column block, one leading-dimension
     //    offset away, is a tile of ones.
     if (lane == 0) {
+      const uint64_t desc_q0 = smem_desc(sQ), desc_k0 = smem_desc(sKV), desc_p0 = smem_desc(sP);
       WAIT(BAR(Q_FULL), 0);
       auto issue_qk = [&](int j) {
         const int st = j % kKVStages, sb = j & 1;
         WAIT(BAR(KV_FULL + st), (j / kKVStages) & 1);
         tc_fence_after();
-        const uint32_t k_base = sKV + st * 2 * kKBytes;
+        // descriptors differ only in their 14-bit start-address field: add to the low word
+        const uint64_t kd = desc_k0 + ((st * 2 * kKBytes) >> 4);
 #pragma unroll
         for (int ks = 0; ks < kHd / 16; ++ks)
-          tc_mma(tmem + kTmemS + sb * 64, smem_desc(sQ + ks * 32), smem_desc(k_base + ks * 32), kIdescQK, ks > 0);
+          tc_mma(tmem + kTmemS + sb * 64, desc_q0 + 2 * ks, kd + 2 * ks, kIdescQK, ks > 0);
         tc_commit(BAR(S_FULL + sb));
       };
       issue_qk(0);
@@ -274,11 +276,11 @@ __global__ void __launch_bounds__(kThreads, 2)
         WAIT(BAR(P_FULL + sb), (j >> 1) & 1);
         tc_fence_after();
         const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
-        const uint32_t p_base = sP + sb * kPBytes;
+        const uint64_t vd = smem_desc(v_base, sOnes - v_base);
+        const uint64_t pd = desc_p0 + ((sb * kPBytes) >> 4);
 #pragma unroll
         for (int kk = 0; kk < kKTile / 16; ++kk)
-          tc_mma(tmem + kTmemO, smem_desc(p_base + kk * 32), smem_desc(v_base + kk * kBox, sOnes - v_base), kIdescPV,
-                 (j | kk) != 0);
+          tc_mma(tmem + kTmemO, pd + 2 * kk, vd + kk * (kBox >> 4), kIdescPV, (j | kk) != 0);
         tc_commit(BAR(KV_EMPTY + st));
         tc_commit(BAR(PV_DONE + sb));
       }
@@ -327,9 +329,16 @@ __global__ void __launch_bounds__(kThreads, 2)
         for (int i = 0; i < kKTile; ++i)
           if (k0 + i > limit) sc[i] = -INFINITY;
       }
-      float mx = sc[0];
+      float mx8[8];
 #pragma unroll
-      for (int i = 1; i < kKTile; ++i) mx = fmaxf(mx, sc[i]);
+      for (int i = 0; i < 8; ++i) mx8[i] = sc[i];
+#pragma unroll
+      for (int i = 8; i < kKTile; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(mx8[u], sc[i + u]);
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       if (j == 0) {
         m_used = mx;                                 // finite: key 0 is visible to every row
       } else if (__any_sync(0xffffffffu, (mx - m_used) * sl2 > kRescaleThreshold)) {
@@ -354,7 +363,8 @@ __global__ void __launch_bounds__(kThreads, 2)
         tc_fence_before();
       }
       const float neg = -m_used * sl2;
-      WAIT(BAR(PV_DONE + sb), ((j >> 1) & 1) ^ 1);   // P buffer free: P_{j-2} V_{j-2} has completed
+      // The P buffer is free: S_FULL_j was committed after P_{j-2} V_{j-2} had been issued by the same
+      // thread, and a commit only arrives once everything issued before it has completed.
       unsigned char* prow = base_ptr + kSmemP + sb * kPBytes + r * 128;
 #pragma unroll
       for (int ch = 0; ch < kKTile / 8; ++ch) {
