@@ -100,8 +100,9 @@ inline int ws_extra_for_bytes(int n_tokens, int q_heads, int kv_heads, int head_
 //   1. take the smallest chunk >= 256 keys whose item count stays within the
 //      budget (one item per token plus `extra_budget`): the most parallelism the
 //      workspace and the target grid allow, without paying a partial per 16 KB;
-//   2. if that still leaves fewer thread blocks than one wave of the GPU, go down
-//      to 128 and then 64 keys while the budget allows.
+//   2. if that still leaves fewer units than the GPU has workers (warps), go down to
+//      128 keys if the budget allows (64-key units were measured slower: the fixed
+//      cost per unit outweighs the extra parallelism).
 // Returns 0 when no candidate fits (tokens are then processed unsplit).
 PKV_HD inline int choose_chunk(const long long* items_at, int n_tokens, int kv_heads, long long extra_budget,
                                int wave_ctas, int forced_chunk) {
@@ -114,10 +115,7 @@ PKV_HD inline int choose_chunk(const long long* items_at, int n_tokens, int kv_h
     if (items_at[j] - n_tokens <= extra_budget) { best = j; break; }
   }
   if (best < 0) return 0;
-  for (int j = 1; j >= 0; --j) {
-    if (items_at[best] * kv_heads >= wave_ctas) break;
-    if (items_at[j] - n_tokens <= extra_budget) best = j;
-  }
+  if (best == 2 && items_at[best] * kv_heads < wave_ctas && items_at[1] - n_tokens <= extra_budget) best = 1;
   return kMinChunk << best;
 }
 
