@@ -12,18 +12,20 @@
 // Roles inside a block of 192 threads:
 //   warp 4 (one lane)   TMA producer: the Q tile once, then per key tile four boxes of
 //                       16 slots x 128 bytes for K and four for V, gathered through the
-//                       block table into a three-stage ring (128-byte swizzle, which is
+//                       block table into a four-stage ring (128-byte swizzle, which is
 //                       also the canonical shared-memory layout of the MMA operands).
 //   warp 5 (one lane)   MMA issuer: S[j] = Q K_j^T (4 MMAs of K=16) into one of two S
-//                       buffers in tensor memory, then O += P_j V_j (4 MMAs, plus 4 narrow
-//                       ones for the row sums); tcgen05.commit signals the mbarriers.
+//                       buffers in tensor memory, then O += P_j V_j (4 MMAs of N = 80 whose A
+//                       operand is read from tensor memory and whose last 16 columns give
+//                       the row sums); tcgen05.commit signals the mbarriers.
 //   warps 0-3           softmax: thread r owns row r (tensor-memory lane r).  The 64 scores
-//                       of the row come to registers with tcgen05.ld (the S buffer is
-//                       released at once), then row max, exp2, P written to shared memory
-//                       in the operand layout; causal mask by absolute position, applied
-//                       only on tiles that reach the diagonal.  O and the row sums (a
-//                       second MMA against a tile of ones) accumulate in tensor memory and
-//                       are rescaled only when a row's maximum has grown by more than 2^8.
+//                       of the row come to registers with tcgen05.ld, then row max, exp2,
+//                       and P goes back with tcgen05.st as packed 16-bit pairs over the
+//                       first 32 columns of the same S buffer; causal mask by absolute
+//                       position, applied only on tiles that reach the diagonal.  O and the
+//                       row sums (the product of P with a tile of ones) accumulate in tensor
+//                       memory and are rescaled only when a row's maximum has grown by more
+//                       than 2^8.
 // S[j+1] is issued before P_j V_j, so the tensor core works on the next scores while
 // the softmax warps are busy with the current ones; shared and tensor memory are
 // sized so that two blocks share an SM and fill each other's bubbles.
@@ -47,16 +49,14 @@ constexpr int kQTile = 128;     // query rows per block
 constexpr int kKTile = 64;      // keys per tile
 constexpr int kHd = 64;         // head_dim this kernel is written for
 constexpr int kThreads = 192;
-constexpr int kKVStages = 3;
+constexpr int kKVStages = 4;
 constexpr int kBox = 16 * 128;                   // one TMA box: 16 slots x 128 bytes
 constexpr int kQBytes = kQTile * 128;            // 128 rows x 128 bytes
 constexpr int kKBytes = kKTile * 128;            // one K (or V, or P) tile: 64 keys x 128 bytes / 128 rows x 64 keys
-constexpr int kPBytes = kQTile * kKTile * 2;     // 128 rows x 64 keys, 16-bit
 constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kSmemQ + kQBytes;                    // kKVStages x (K, V)
-constexpr int kSmemP = kSmemKV + kKVStages * 2 * kKBytes;    // 2 buffers
-constexpr int kSmemOnes = kSmemP + 2 * kPBytes;              // a V-shaped tile of 1.0: P x ones = row sums
-constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 105 KB: two blocks per SM
+constexpr int kSmemOnes = kSmemKV + kKVStages * 2 * kKBytes; // a V-shaped tile of 1.0: P x ones = row sums
+constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 89 KB: two blocks per SM
 constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
 constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64) with the row sums right behind (16)
 constexpr float kRescaleThreshold = 8.f;                     // in log2 units: P stays below 2^8
@@ -84,6 +84,21 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// A operand in tensor memory (row i of A in lane i, two 16-bit elements per column).
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -136,6 +151,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Three-input maximum: one instruction on this architecture.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ void give_up() { atomicOr(&g_pkv_prefill_error, 4u); }
 
 template <typename T>
@@ -148,16 +170,16 @@ __global__ void __launch_bounds__(kThreads, 2)
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[13];
+  __shared__ __align__(8) unsigned long long bars[1 + 2 * kKVStages + 6];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sP = base + kSmemP, sOnes = base + kSmemOnes;
+  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sOnes = base + kSmemOnes;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 4, S_FULL = 7, P_FULL = 9, PV_DONE = 11 };
+  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = KV_FULL + kKVStages, S_FULL = KV_EMPTY + kKVStages, P_FULL = S_FULL + 2, PV_DONE = P_FULL + 2 };
 
   // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
   if (threadIdx.x == 0) {
@@ -169,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     for (int i = 0; i < 2; ++i) {
       mbar_init(BAR(S_FULL + i), 1);     // tcgen05.commit after Q K_j^T
       mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P
-      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated, P buffer free
+      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated
     }
     mbar_fence_init();
   }
@@ -247,16 +269,19 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   } else if (warp == 5) {
     // ================================ MMA issuer ================================
-    // One thread issues everything, and every mbarrier wait and every tcgen05 instruction it
-    // executes costs it a few hundred cycles, so the schedule is kept to two waits, eight MMAs
-    // and three commits per key tile:
-    //  * no separate "S buffer free" barrier: a softmax thread reads S_{j-1} before it arrives on
-    //    P_FULL_{j-1}, which this thread has waited for before it overwrites that buffer with S_{j+1};
+    // One thread issues everything.  A tcgen05.mma returns to the issuing thread at the rate the
+    // tensor pipe retires them (48 cycles for 128 x 64 x 16 from shared memory, 45 with A in tensor
+    // memory), a blocking try_wait costs a few hundred cycles even on a completed phase (mbar_wait
+    // looks first), and the scalar code of a lone thread runs at one dependent instruction every
+    // few cycles, so the schedule is kept to two waits, eight MMAs and three commits per key tile:
+    //  * no separate "S buffer free" barrier: a softmax thread has read S_{j-1} and written P_{j-1}
+    //    over it before it arrives on P_FULL_{j-1}; this thread waits for that, issues P_{j-1} V_{j-1},
+    //    and only then S_{j+1} into the same buffer (instructions of one thread execute in order);
     //  * O += P V and the row sums of P come out of ONE MMA of N = 80: the B operand is MN-major,
     //    its first 64 columns are the V tile and its next column block, one leading-dimension
     //    offset away, is a tile of ones.
     if (lane == 0) {
-      const uint64_t desc_q0 = smem_desc(sQ), desc_k0 = smem_desc(sKV), desc_p0 = smem_desc(sP);
+      const uint64_t desc_q0 = smem_desc(sQ), desc_k0 = smem_desc(sKV);
       WAIT(BAR(Q_FULL), 0);
       auto issue_qk = [&](int j) {
         const int st = j % kKVStages, sb = j & 1;
@@ -277,10 +302,10 @@ __global__ void __launch_bounds__(kThreads, 2)
         tc_fence_after();
         const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
         const uint64_t vd = smem_desc(v_base, sOnes - v_base);
-        const uint64_t pd = desc_p0 + ((sb * kPBytes) >> 4);
+        const uint32_t p_addr = tmem + kTmemS + sb * 64;      // P(j) lies over the first 32 columns of S(j)
 #pragma unroll
         for (int kk = 0; kk < kKTile / 16; ++kk)
-          tc_mma(tmem + kTmemO, pd + 2 * kk, vd + kk * (kBox >> 4), kIdescPV, (j | kk) != 0);
+          tc_mma_ts(tmem + kTmemO, p_addr + kk * 8, vd + kk * (kBox >> 4), kIdescPV, (j | kk) != 0);
         tc_commit(BAR(KV_EMPTY + st));
         tc_commit(BAR(PV_DONE + sb));
       }
@@ -329,16 +354,15 @@ __global__ void __launch_bounds__(kThreads, 2)
         for (int i = 0; i < kKTile; ++i)
           if (k0 + i > limit) sc[i] = -INFINITY;
       }
+      // Row maximum: eight independent chains of three-input maxima, two scores a step.
       float mx8[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx8[i] = sc[i];
+      for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(sc[u], sc[8 + u]);
 #pragma unroll
-      for (int i = 8; i < kKTile; i += 8) {
+      for (int i = 16; i < kKTile; i += 16)
 #pragma unroll
-        for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(mx8[u], sc[i + u]);
-      }
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        for (int u = 0; u < 8; ++u) mx8[u] = max3(mx8[u], sc[i + u], sc[i + 8 + u]);
+      const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), fmaxf(max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       if (j == 0) {
         m_used = mx;                                 // finite: key 0 is visible to every row
       } else if (__any_sync(0xffffffffu, (mx - m_used) * sl2 > kRescaleThreshold)) {
@@ -363,16 +387,16 @@ __global__ void __launch_bounds__(kThreads, 2)
         tc_fence_before();
       }
       const float neg = -m_used * sl2;
-      // The P buffer is free: S_FULL_j was committed after P_{j-2} V_{j-2} had been issued by the same
-      // thread, and a commit only arrives once everything issued before it has completed.
-      unsigned char* prow = base_ptr + kSmemP + sb * kPBytes + r * 128;
+      // P goes back into tensor memory as packed 16-bit pairs over the first 32 columns of the S
+      // buffer it came from: this thread has all of its own row in registers, and the MMA thread
+      // overwrites the buffer with S(j+2) only after it has issued P(j) V(j).
 #pragma unroll
-      for (int ch = 0; ch < kKTile / 8; ++ch) {
-        float p[8];
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) p[i] = ex2_approx(fmaf(sc[ch * 8 + i], sl2, neg));
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
-            make_uint4(pack2<T>(p[0], p[1]), pack2<T>(p[2], p[3]), pack2<T>(p[4], p[5]), pack2<T>(p[6], p[7]));
+        for (int i = 0; i < 16; ++i)
+          pk[i] = pack2<T>(ex2_approx(fmaf(sc[c * 32 + 2 * i], sl2, neg)), ex2_approx(fmaf(sc[c * 32 + 2 * i + 1], sl2, neg)));
+        tc_st16(tmem + lane_addr + kTmemS + sb * 64 + c * 16, pk);
       }
       if (j == n_kt - 1 && kv_total - k0 < kKTile) {
         // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
@@ -384,8 +408,11 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vrow + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the cleared rows before the MMA reads them
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // P (ones, V) stores before the MMA reads them
+      if (j == 0) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tile of ones, likewise
+      tc_wait_st();
+      tc_fence_before();
       mbar_arrive(BAR(P_FULL + sb));
     }
     // epilogue: O / row sum

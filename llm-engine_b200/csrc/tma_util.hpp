@@ -72,11 +72,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll itself blocks for a
-// hardware-defined time slice) and reports failure instead of spinning forever.
+// Non-blocking look at a phase: a few tens of cycles, where try_wait costs a few hundred even
+// when the phase has long completed.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: a quick look first, then up to `limit` blocking polls (each blocks for a
+// hardware-defined time slice); reports failure instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 17)) {
+  if (mbar_test(bar, parity)) return true;
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// Bounded busy wait for a single latency-critical thread: it never sleeps, so it sees the phase
+// flip within one poll.
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_test(bar, parity)) return true;
   return false;
 }
 // ---- TMA: one box of a 2-D tensor map into this block's shared memory ---------------
