@@ -619,19 +619,36 @@ def run_prefix_cow(args, rank, local_rank, world):
     plan = pkv.DecodePlan(S, qh, kvh, hd, device=dev)
     i32 = lambda x: torch.from_numpy(np.ascontiguousarray(x, dtype=np.int32)).to(dev, non_blocking=True)
 
+    # Index build on the device (pkv_step_pack_device): the tables stay resident, a step sends only
+    # the newly appended block ids and one (row, position, 1) triple per sequence.  --host-pack uses the
+    # host routine and five copies per step instead, as the reference does.
+    max_row = max(t.num_blocks() for t in seqs) + 8
+    packer = pkv.DeviceStepPacker(S, max_row, bs, max_tokens=S, max_table_entries=S * max_row, device=dev)
+    for i, t in enumerate(seqs):
+        packer.set_table(i, t.blocks)
+
     def decode_step():
-        for t, n in zip(seqs, lens):
-            mgr.ensure_slot(t, n + 1)
-        idx = pkv.pack_step([t.blocks for t in seqs], lens, bs, tok_keys=list(range(S)))
-        d = [i32(idx.block_tables), i32(idx.table_offset), i32(idx.token_seq), i32(idx.token_pos)]
-        d_slots = i32(idx.slots)
-        plan.build_host(idx.token_pos)
+        if args.host_pack:
+            for t, n in zip(seqs, lens):
+                mgr.ensure_slot(t, n + 1)
+            idx = pkv.pack_step([t.blocks for t in seqs], lens, bs, tok_keys=list(range(S)))
+            d = [i32(idx.block_tables), i32(idx.table_offset), i32(idx.token_seq), i32(idx.token_pos)]
+            d_slots = i32(idx.slots)
+            plan.build_host(idx.token_pos)
+        else:
+            for i, (t, n) in enumerate(zip(seqs, lens)):
+                mgr.ensure_slot(t, n + 1)
+                if n % bs == 0:                       # position n opened a new block
+                    packer.set_block(i, n // bs, int(t.blocks[-1]))
+            packer.pack([(i, lens[i], 1) for i in range(S)])
+            d = [packer.tables, packer.table_offset, packer.token_seq, packer.positions]
+            d_slots = packer.slots
+            plan.build_device(packer.positions)
         for l in range(L):
             pkv.launch_store_kv(k[l], v[l], d_slots, pools[l, 0], pools[l, 1], S, kv_dim)
             plan.attention(q[l], pools[l, 0], pools[l, 1], *d, out[l], bs, scale)
         for i in range(S):
             lens[i] += 1
-        return idx
 
     for _ in range(3):
         decode_step()
@@ -653,6 +670,7 @@ def run_prefix_cow(args, rank, local_rank, world):
             "value": S / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"cfg5: {WORKLOAD_TEXT['cfg5']}", "layers": L, "launch": "eager launches, host bookkeeping in the timed region",
+                       "index_build": "host (pkv_step_pack + five copies)" if args.host_pack else "device (pkv_step_pack_device, one copy)",
                        "note": "the reference never shares a partial block (docs/design.md:36); the CoW trigger is this library's additive fork()/cow()"},
             "cow": {"pairs": len(pairs), "pools": 2 * L, "us_per_wave": cow_us, "bytes_read_plus_written": cow_bytes,
                     "GBps": cow_bytes / cow_us / 1e3, "frac_of_measured_hbm": cow_bytes / cow_us / 1e3 / peak},
@@ -675,6 +693,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--host-pack", action="store_true", help="cfg5: build the step indices on the host instead of on the device")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling runs only; noted in config)")
     args = ap.parse_args()

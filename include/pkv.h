@@ -255,6 +255,33 @@ int pkv_step_pack(int n_tokens, const uint64_t* tok_seq_key, const int32_t* cons
                   int* token_seq, int* tables, size_t tables_cap, int* table_offset,
                   size_t offsets_cap, int* n_seqs, int* n_table);
 
+/* ------------------------------------------------------------------ f2 ----
+ * Step-index build on the device.  Replaces all of CudaModel::upload_step_indices
+ * (src/model/cuda/cuda_model.cu:453-491): its O(N*S) host loop and its six
+ * synchronous host-to-device copies per step, which is what stands between the
+ * caller and a CUDA-graph decode step.  Every sequence's block table lives in one
+ * row of a device-resident store d_seq_tables[max_rows][table_stride] with its
+ * length in d_seq_nblocks[max_rows] (zero-initialised by the caller).  Per step the
+ * host sends two small arrays of int32 triples (one copy, if it packs them in one
+ * buffer):
+ *   d_updates[n_updates][3] = { row, block_index, block_id }: that entry of the row
+ *       is set and the row's length raised to block_index + 1; block_index = -1
+ *       releases the row (length 0).  Releases are applied before sets.
+ *   d_slices[n_slices][3]   = { row, first_position, length }: the step's packed
+ *       tokens, slice after slice (a decode token is a slice of length 1).
+ * Outputs, identical to what pkv_step_pack writes for the same tokens: positions,
+ * token_seq, slots [sum of lengths], tables (each distinct row's table once, in order
+ * of first appearance), table_offset [distinct rows]; d_counts[4] = { n_tokens,
+ * n_seqs, n_table, status }, status = 0 or a bit set: 1 tables_cap too small,
+ * 2 tokens_cap too small (nothing is written in those two cases), 4 a position
+ * beyond its row's table (its slot is written as 0), 8 a row or block index out of
+ * range (ignored).  One launch, nothing synchronises; at most 4096 slices. */
+int pkv_step_pack_device(const int32_t* d_updates, int n_updates, const int32_t* d_slices, int n_slices,
+                         int32_t* d_seq_tables, int32_t* d_seq_nblocks, int max_rows, int table_stride,
+                         int block_size, int32_t* d_slots, int32_t* d_token_seq, int32_t* d_positions,
+                         int tokens_cap, int32_t* d_tables, int tables_cap, int32_t* d_table_offset,
+                         int32_t* d_counts, pkv_stream stream);
+
 /* ------------------------------------------------------------------ a0 ----
  * KV block bookkeeping (host).  C handles over the C++ KVCacheManager / BlockTable
  * of include/pkv_kv_cache.hpp, which keep the public surface of llm-engine's

@@ -48,6 +48,7 @@ SIGNATURES = {
     **{f"pkv_prefill_attn_{s}": (_i, [_vp] * 9 + [_i] * 8 + [_f, _vp]) for s in ("f16", "bf16")},
     **{f"pkv_copy_blocks_{s}": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]) for s in ("f16", "bf16", "f32")},
     "pkv_copy_blocks_layers": (_i, [_vp, _i, _vp, _i, _sz, _vp]),
+    "pkv_step_pack_device": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp]),
     "pkv_step_pack": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _vp]),
     "pkv_kvmgr_create": (_vp, [_i, _i, _i]),
     "pkv_kvmgr_destroy": (None, [_vp]),

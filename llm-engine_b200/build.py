@@ -22,6 +22,7 @@ SOURCES = [
     "append.cu",
     "copy_blocks.cu",
     "rope_append.cu",
+    "step_pack.cu",
     "decode_attn.cu",
     "prefill_attn.cu",
     "engine_shim.cu",
