@@ -563,6 +563,61 @@ def run_prefill(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def long_prompt_tables(S, prefix_blocks, bs, seed=1240):
+    """S sequences that share prefix_blocks leading blocks and have 32..256 tokens of their own."""
+    rng = np.random.default_rng(seed)
+    ctx = prefix_blocks * bs + rng.integers(32, 257, size=S)
+    own = (ctx + 1 + bs - 1) // bs - prefix_blocks
+    nb = int(own.sum()) + prefix_blocks + 8
+    perm = rng.permutation(nb).astype(np.int32)
+    tables, at = [], prefix_blocks
+    for n in own:
+        tables.append(np.concatenate([perm[:prefix_blocks], perm[at:at + n]]).astype(np.int32))
+        at += n
+    return tables, ctx.tolist()
+
+
+def compare_shared_plan(pkv, torch, dev, tables, positions, qh, kvh, hd, bs, nb, layers):
+    """us per layer of attention + merge with the ordinary plan and with the shared-prefix plan."""
+    S = len(tables)
+    nb = nb or int(max(int(t.max()) for t in tables)) + 1
+    kv_dim, H = kvh * hd, qh * hd
+    idx = pkv.pack_step(tables, positions, bs, tok_keys=list(range(S)))
+    pools = torch.randn((layers, 2, nb * bs, kv_dim), device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q = torch.randn((layers, S, H), device=dev, dtype=torch.float32).to(torch.bfloat16)
+    out = torch.zeros((layers, S, H), device=dev, dtype=torch.bfloat16)
+    i32 = lambda x: torch.from_numpy(np.ascontiguousarray(x, dtype=np.int32)).to(dev)
+    d = [i32(idx.block_tables), i32(idx.table_offset), i32(idx.token_seq), i32(idx.token_pos)]
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    res = {"per_sequence_bytes_per_layer": int(sum(2 * (p + 1) * kv_dim * 2 for p in positions))}
+    for name in ("ordinary", "shared"):
+        pl = pkv.DecodePlan(S, qh, kvh, hd, device=dev)
+        pl.build_host(idx.token_pos) if name == "ordinary" else pl.build_host_shared(idx, bs, min_saved_bytes=0)
+
+        def run_layers():
+            for l in range(layers):
+                pl.attention(q[l], pools[l, 0], pools[l, 1], *d, out[l], bs, 1.0 / float(np.sqrt(hd)))
+        for _ in range(3):
+            run_layers()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run_layers()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(20):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        res[name] = {"us_per_layer": a.elapsed_time(b) / 20 / layers * 1e3, "shared_units": pl.n_shared_units,
+                     "items": int(pl.plan.n_items), "chunk": int(pl.plan.chunk)}
+    pl = pkv.DecodePlan(S, qh, kvh, hd, device=dev)
+    res["default_rule_picks"] = "shared" if pl.build_host_shared(idx, bs).n_shared_units > 0 else "ordinary"
+    return res
+
+
 def run_prefix_cow(args, rank, local_rank, world):
     """--workload cfg5: 128 sequences forked from one parent that holds a 512-token prefix plus a partial
     block; the first divergent write of each child triggers a copy-on-write block copy on every pool
@@ -666,6 +721,15 @@ def run_prefix_cow(args, rank, local_rank, world):
     wall = time.perf_counter() - t0
     ms_step = a.elapsed_time(b) / steps
     peak, src = peaks()
+    # Shared-prefix-aware plan against the ordinary one (attention + merge per layer, indices and plan
+    # resident, CUDA-graph replay, CUDA events): on the state the 64 steps left, and on a long shared
+    # prompt where the saving outweighs the extra launch.
+    del pools, q, k, v, out
+    torch.cuda.empty_cache()
+    shared_cmp = {"cfg5_after_64_steps": compare_shared_plan(pkv, torch, dev, [np.asarray(t.blocks) for t in seqs],
+                                                             [n - 1 for n in lens], qh, kvh, hd, bs, nb, min(L, 4)),
+                  "long_prompt_256_seqs_x_8192_shared": compare_shared_plan(pkv, torch, dev, *long_prompt_tables(256, 512, bs),
+                                                                            qh, kvh, hd, bs, None, min(L, 4))}
     line = {"metric": "prefix-cache decode tok/s (bookkeeping + append + paged decode attention, 64 steps) and CoW copy GB/s",
             "value": S / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -677,6 +741,7 @@ def run_prefix_cow(args, rank, local_rank, world):
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_combine_kernel (whole step incl. host)",
                          "achieved": byts / steps / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": byts / steps / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src},
+            "shared_prefix_plan": shared_cmp,
             "cpu_baseline": None, "e2e": {"value": S * steps / wall, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                                           "note": "wall clock over the same 64 steps"},
             "gpu_launches": 3 * L * steps}

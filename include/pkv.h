@@ -171,7 +171,7 @@ typedef struct pkv_decode_plan {
   int chunk;      /* keys per work item; 0 = no splitting */
   int n_items;    /* exact item count when host-built, upper bound when device-built */
   int exact;      /* 1 if n_items is exact */
-  int reserved;   /* internal: non-zero when some token was split */
+  int reserved;   /* internal: bit 0 set when some token was split; the other bits count shared-prefix units */
 } pkv_decode_plan;
 
 size_t pkv_decode_plan_staging_bytes(int n_tokens, int kv_heads);
@@ -181,6 +181,28 @@ int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int 
 int pkv_decode_plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
                            void* workspace, size_t workspace_bytes, pkv_stream stream,
                            pkv_decode_plan* plan);
+/* f3: shared-prefix-aware plan.  llm-engine's prefix cache makes sequences with a
+ * common prompt share their leading blocks (KVCacheManager::allocate_prompt,
+ * src/kv_cache/block_allocator.cpp:28-78), yet its decode kernels fetch those
+ * blocks once per sequence.  Given the host copies of the step's index arrays (the
+ * outputs of pkv_step_pack: token_seq, the concatenated tables, table_offset),
+ * this planner finds the decode tokens whose sequences start with the same blocks
+ * and covers that range with units that fetch K/V once for up to four tokens; each
+ * token's own remaining range is planned as usual and the partials are merged by
+ * the same kernel.  The plan is consumed by pkv_decode_attn_planned_* exactly like
+ * one from pkv_decode_plan_host; results agree with it to rounding (the same
+ * keys, grouped differently).  Geometries the shared units do not cover (head_dim
+ * other than 64, more than 8 query heads per kv head, block_size not a power of
+ * two >= 16, fp32 K/V) and steps without shared prefixes get the ordinary plan, and
+ * so do steps whose shared units would save fewer than min_saved_bytes of K/V reads
+ * per layer (-1: the library's default, 128 MiB, below which the extra launch costs
+ * more than the reads it saves on a B200; 0: always use them). */
+int pkv_decode_plan_host_shared(const int* h_token_pos, const int* h_token_seq, const int* h_tables,
+                                const int* h_table_offset, int n_tokens, int n_seqs, int n_table,
+                                int block_size, int q_heads, int kv_heads, int head_dim,
+                                long long min_saved_bytes, void* h_staging, size_t staging_bytes,
+                                void* workspace, size_t workspace_bytes, pkv_stream stream,
+                                pkv_decode_plan* plan);
 int pkv_decode_attn_planned_f16(const pkv_decode_plan* plan, const void* q, const void* k_cache,
                                 const void* v_cache, const int* block_tables, const int* table_offset,
                                 const int* token_seq, const int* token_pos, void* out, int block_size,

@@ -43,6 +43,8 @@ SIGNATURES = {
     "pkv_decode_plan_staging_bytes": (_sz, [_i, _i]),
     "pkv_decode_plan_host": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
     "pkv_decode_plan_device": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
+    "pkv_decode_plan_host_shared": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, C.c_longlong, _vp, _sz, _vp, _sz, _vp,
+                                         C.POINTER(DecodePlan)]),
     **{f"pkv_decode_attn_planned_{s}": (_i, [C.POINTER(DecodePlan)] + [_vp] * 8 + [_i, _f, _vp, _sz, _vp])
        for s in ("f16", "bf16", "f32")},
     **{f"pkv_prefill_attn_{s}": (_i, [_vp] * 9 + [_i] * 8 + [_f, _vp]) for s in ("f16", "bf16")},

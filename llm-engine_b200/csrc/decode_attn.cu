@@ -182,10 +182,10 @@ int persistent_sms() {
   return sms;
 }
 
-template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MINB>
+template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MINB, int TOK = 1>
 int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
   using S = TmaSmem<D, MT, NSTAGES, WARPS>;
-  auto kern = decode_tma_kernel<T, D, NT, MT, NSTAGES, WARPS, MINB>;
+  auto kern = decode_tma_kernel<T, D, NT, MT, NSTAGES, WARPS, MINB, TOK>;
   static thread_local int configured_device = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -278,10 +278,27 @@ int launch_decode_main(const DecodeArgs& a, int grid, cudaStream_t stream, bool*
   return launch_simt<T, 8>(a, grid, stream);
 }
 
-// Attention kernel, then (when the plan split any token) the merge of the partials.
+// Whether the geometry runs on the TMA kernel (the only one that takes shared-prefix units).
+template <typename T>
+bool shared_units_ok(const DecodeArgs& a) {
+  if constexpr (IsF32<T>::value) return false;
+  return a.head_dim == 64 && a.group <= 8 && a.bs_log2 >= 4 && a.scale > 0.f && tuning().use_tma && tensor_map_encoder() != nullptr;
+}
+
+// Shared-prefix units first (one K/V fetch for up to four tokens), then the attention kernel
+// over the ordinary items, then (when the plan split any token) the merge of the partials.
 template <typename T>
 int launch_decode(const DecodeArgs& a, int grid, cudaStream_t stream, bool has_splits) {
   bool log2_domain = true;
+  if constexpr (!IsF32<T>::value) {
+    if (a.n_shared > 0) {
+      long long units = static_cast<long long>(a.n_shared) * a.kv_heads;
+      if (units > 0x7fffffffll) units = 0x7fffffffll;
+      // <T, head_dim, head tiles (4 tokens x 1), 16-key tiles per stage, stages, warps, blocks per SM, tokens per unit>
+      const int st = launch_tma<T, 64, 4, 2, 2, 4, 2, 4>(a, static_cast<int>(units), stream);
+      if (st != PKV_OK) return st;
+    }
+  }
   const int st = launch_decode_main<T>(a, grid, stream, &log2_domain);
   if (st != PKV_OK || !has_splits) return st;
   return log2_domain ? launch_combine<T, true>(a, stream) : launch_combine<T, false>(a, stream);
@@ -328,6 +345,8 @@ void fill_args(DecodeArgs& a, const void* q, const void* kc, const void* vc, con
   a.header = nullptr; a.items = nullptr; a.tok_split = nullptr; a.counters = nullptr;
   a.part_ml = nullptr; a.part_acc = nullptr;
   a.direct = 1;
+  a.shared_items = nullptr;
+  a.n_shared = 0;
 }
 
 void attach_workspace(DecodeArgs& a, void* workspace, const WsLayout& w) {
@@ -402,10 +421,18 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
   DecodeArgs a;
   fill_args(a, q, kc, vc, bt, to, ts, tp, out, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size, scale);
   attach_workspace(a, workspace, w);
+  const int n_shared = plan->reserved >> 1;
+  if (n_shared > 0) {
+    if (!shared_units_ok<T>(a))
+      return fail(PKV_E_UNSUPPORTED, "%s: a plan with shared-prefix units needs 16-bit K/V, head_dim 64, at most 8 query heads per kv head "
+                  "and a power-of-two block_size >= 16", fn);
+    a.shared_items = reinterpret_cast<const int4*>(a.items + plan->n_items);
+    a.n_shared = n_shared;
+  }
   long long blocks = static_cast<long long>(plan->n_items) * plan->kv_heads;
   if (!plan->exact && blocks > persistent_grid()) blocks = persistent_grid();
   if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
-  return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream), plan->reserved != 0);
+  return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream), (plan->reserved & 1) != 0);
 }
 
 template <typename T>
@@ -534,6 +561,175 @@ int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int 
   plan->n_items = ni;
   plan->exact = 1;
   plan->reserved = np > 0 ? 1 : 0;       // whether any token was split (the merge kernel is skipped otherwise)
+  return PKV_OK;
+}
+
+int pkv_decode_plan_host_shared(const int* h_token_pos, const int* h_token_seq, const int* h_tables,
+                                const int* h_table_offset, int n_tokens, int n_seqs, int n_table, int block_size,
+                                int q_heads, int kv_heads, int head_dim, long long min_saved_bytes, void* h_staging,
+                                size_t staging_bytes, void* workspace, size_t workspace_bytes, pkv_stream stream,
+                                pkv_decode_plan* plan) {
+  const char* fn = "pkv_decode_plan_host_shared";
+  if (!plan) return fail(PKV_E_ARG, "%s: null plan", fn);
+  std::memset(plan, 0, sizeof(*plan));
+  if (n_tokens <= 0) return PKV_OK;
+  if (!h_token_pos || !h_token_seq || !h_tables || !h_table_offset || !h_staging || !workspace)
+    return fail(PKV_E_ARG, "%s: null pointer", fn);
+  int st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, block_size);
+  if (st != PKV_OK) return st;
+  if (n_seqs <= 0 || n_table < 0) return fail(PKV_E_ARG, "%s: n_seqs %d, n_table %d", fn, n_seqs, n_table);
+  const int bsl = log2_exact(block_size);
+  // Shared units run on the TMA kernel only; any other geometry gets the ordinary plan.
+  if (head_dim != 64 || q_heads / kv_heads > 8 || bsl < 4)
+    return pkv_decode_plan_host(h_token_pos, n_tokens, q_heads, kv_heads, head_dim, h_staging, staging_bytes, workspace,
+                                workspace_bytes, stream, plan);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PKV_E_ARG, "%s: workspace must be 256-byte aligned", fn);
+  WsLayout w;
+  const int budget = plan_budget(n_tokens, q_heads, kv_heads, head_dim, workspace_bytes, &w);
+  if (budget < 0) return fail(PKV_E_WORKSPACE, "%s: workspace of %zu bytes cannot hold the plan for %d tokens", fn, workspace_bytes, n_tokens);
+
+  // ---- 1. which tokens share a prefix: sequences with the same first block form a cluster; what the
+  //         cluster shares is the longest run of leading blocks common to all its members, cut below
+  //         every member's own position (a token's newest key is never shared) ----
+  constexpr int kMinShared = 64;                // keys; below this a shared unit is not worth its partial
+  std::vector<int> seq_tokens(n_seqs, 0);
+  for (int t = 0; t < n_tokens; ++t) {
+    if (h_token_pos[t] < 0) return fail(PKV_E_ARG, "%s: token %d has negative position %d", fn, t, h_token_pos[t]);
+    if (h_token_seq[t] < 0 || h_token_seq[t] >= n_seqs) return fail(PKV_E_ARG, "%s: token %d names sequence %d of %d", fn, t, h_token_seq[t], n_seqs);
+    ++seq_tokens[h_token_seq[t]];
+  }
+  auto table_len = [&](int s) { return (s + 1 < n_seqs ? h_table_offset[s + 1] : n_table) - h_table_offset[s]; };
+  std::vector<int> order;                       // decode tokens (one per sequence), sorted by first block
+  for (int t = 0; t < n_tokens; ++t) {
+    const int s = h_token_seq[t];
+    if (seq_tokens[s] == 1 && table_len(s) > 0 && h_token_pos[t] >= kMinShared) order.push_back(t);
+  }
+  auto first_block = [&](int t) { return h_tables[h_table_offset[h_token_seq[t]]]; };
+  std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return first_block(x) < first_block(y); });
+  std::vector<int> shared_len(n_tokens, 0);     // keys of token t that a shared unit covers
+  struct Group { int n_tok; int tok[kSharedTokens]; int len; };
+  std::vector<Group> groups;
+  for (size_t i = 0; i < order.size();) {
+    size_t j = i + 1;
+    while (j < order.size() && first_block(order[j]) == first_block(order[i])) ++j;
+    if (j - i >= 2) {
+      const int* t0 = h_tables + h_table_offset[h_token_seq[order[i]]];
+      int lcp = table_len(h_token_seq[order[i]]), min_pos = h_token_pos[order[i]];
+      for (size_t m = i + 1; m < j; ++m) {
+        const int s = h_token_seq[order[m]];
+        const int* tm = h_tables + h_table_offset[s];
+        const int lim = std::min(lcp, table_len(s));
+        int b = 0;
+        while (b < lim && tm[b] == t0[b]) ++b;
+        lcp = b;
+        min_pos = std::min(min_pos, h_token_pos[order[m]]);
+      }
+      const long long keys = std::min<long long>(static_cast<long long>(lcp) << bsl, min_pos);
+      const int len = static_cast<int>(keys) & ~15;
+      if (len >= kMinShared) {
+        size_t m = i;
+        while (j - m >= 2) {                    // groups of four; a remainder of one stays an ordinary token
+          Group g;
+          g.n_tok = static_cast<int>(std::min<size_t>(kSharedTokens, j - m));
+          if (j - m == kSharedTokens + 1) g.n_tok = 3;   // 5 = 3 + 2 rather than 4 + 1
+          g.len = len;
+          for (int k = 0; k < kSharedTokens; ++k) g.tok[k] = k < g.n_tok ? order[m + k] : order[m];
+          for (int k = 0; k < g.n_tok; ++k) shared_len[order[m + k]] = len;
+          groups.push_back(g);
+          m += g.n_tok;
+        }
+      }
+    }
+    i = j;
+  }
+  // Shared units cost one more launch and a few more partials per token; they pay once the K/V reads
+  // they save outweigh that (measured on B200: about 128 MiB per layer, where a 126 MB L2 already
+  // serves most re-reads of a small shared prefix).
+  long long saved = 0;
+  for (const Group& g : groups) saved += static_cast<long long>(g.len) * (g.n_tok - 1) * kv_heads * head_dim * 2 * 2;
+  if (min_saved_bytes < 0) min_saved_bytes = 128ll << 20;
+  if (groups.empty() || saved < min_saved_bytes)
+    return pkv_decode_plan_host(h_token_pos, n_tokens, q_heads, kv_heads, head_dim, h_staging, staging_bytes, workspace,
+                                workspace_bytes, stream, plan);
+
+  // ---- 2. chunk size: the ordinary rule over the ranges that are left, shared ranges counted once ----
+  long long items_at[kNumChunkCandidates] = {0};
+  auto count = [&](int len) {
+    if (len > 0)
+      for (int j = 0; j < kNumChunkCandidates; ++j) items_at[j] += (len + (kMinChunk << j) - 1) / (kMinChunk << j);
+  };
+  for (int t = 0; t < n_tokens; ++t) count(h_token_pos[t] + 1 - shared_len[t]);
+  for (const Group& g : groups) count(g.len);
+  int chunk = choose_chunk(items_at, n_tokens, kv_heads, budget, tuning().wave_ctas, tuning().forced_chunk);
+  const int eff_chunk = chunk > 0 ? chunk : 0x40000000;
+  auto nchunks = [&](int len) { return (len + eff_chunk - 1) / eff_chunk; };
+
+  // ---- 3. partial slots per token: its shared chunks first, then its own ----
+  char* img = static_cast<char*>(h_staging);
+  if (w.off_items > staging_bytes) return fail(PKV_E_WORKSPACE, "%s: staging buffer of %zu bytes is too small", fn, staging_bytes);
+  std::memset(img, 0, w.off_items);
+  PlanHeader* hd = reinterpret_cast<PlanHeader*>(img);
+  TokSplit* tsp = reinterpret_cast<TokSplit*>(img + w.off_tok);
+  long long n_items = 0, n_shared = 0;
+  int np = 0;
+  for (int t = 0; t < n_tokens; ++t) {
+    const int own = h_token_pos[t] + 1 - shared_len[t];
+    const int ns = nchunks(shared_len[t]) + nchunks(own);
+    tsp[t] = TokSplit{np, ns};
+    if (ns > 1) np += ns;
+    n_items += nchunks(own);
+  }
+  for (const Group& g : groups) n_shared += nchunks(g.len);
+  const size_t image = w.off_items + sizeof(WorkItem) * static_cast<size_t>(n_items + 3 * n_shared);
+  if (n_items + 3 * n_shared > w.cap_items || np > w.cap_parts || image > staging_bytes)   // no room: the ordinary plan
+    return pkv_decode_plan_host(h_token_pos, n_tokens, q_heads, kv_heads, head_dim, h_staging, staging_bytes, workspace,
+                                workspace_bytes, stream, plan);
+  WorkItem* it = reinterpret_cast<WorkItem*>(img + w.off_items);
+  int ni = 0;
+  for (int t = 0; t < n_tokens; ++t) {          // full chunks first ...
+    const int own = h_token_pos[t] + 1 - shared_len[t], nsc = nchunks(shared_len[t]), nx = nchunks(own);
+    for (int s = 0; s < nx; ++s) {
+      const int len = std::min(eff_chunk, own - s * eff_chunk);
+      if (len == eff_chunk) it[ni++] = WorkItem{t, shared_len[t] + s * eff_chunk, len, tsp[t].nsplits > 1 ? tsp[t].part_base + nsc + s : -1};
+    }
+  }
+  const int n_full = ni;
+  for (int t = 0; t < n_tokens; ++t) {          // ... then the ragged tails, longest first
+    const int own = h_token_pos[t] + 1 - shared_len[t], nsc = nchunks(shared_len[t]), nx = nchunks(own);
+    if (nx == 0) continue;
+    const int b = (nx - 1) * eff_chunk, len = own - b;
+    if (len == eff_chunk) continue;
+    it[ni++] = WorkItem{t, shared_len[t] + b, len, tsp[t].nsplits > 1 ? tsp[t].part_base + nsc + nx - 1 : -1};
+  }
+  std::stable_sort(it + n_full, it + ni, [](const WorkItem& x, const WorkItem& y) { return x.kv_len > y.kv_len; });
+  SharedItem* sh = reinterpret_cast<SharedItem*>(it + ni);
+  int nsh = 0;
+  for (const Group& g : groups)
+    for (int c = 0; c < nchunks(g.len); ++c) {
+      SharedItem x;
+      x.kv_begin = c * eff_chunk;
+      x.kv_len = std::min(eff_chunk, g.len - c * eff_chunk);
+      x.n_tok = g.n_tok;
+      x.pad = 0;
+      for (int k = 0; k < kSharedTokens; ++k) {
+        x.token[k] = g.tok[k];
+        x.part[k] = tsp[g.tok[k]].part_base + c;
+      }
+      sh[nsh++] = x;
+    }
+  hd->magic = kPlanMagic;
+  hd->n_items = ni;
+  hd->chunk = chunk;
+  hd->n_tokens = n_tokens;
+  hd->n_parts = np;
+  hd->kv_heads = kv_heads;
+  cudaError_t e = cudaMemcpyAsync(workspace, img, image, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: plan upload failed: %s", fn, cudaGetErrorString(e));
+  plan->n_tokens = n_tokens; plan->q_heads = q_heads; plan->kv_heads = kv_heads; plan->head_dim = head_dim;
+  plan->chunk = chunk;
+  plan->n_items = ni;
+  plan->exact = 1;
+  plan->reserved = (np > 0 ? 1 : 0) | (nsh << 1);   // bit 0: some token was split; the rest: shared units behind the items
   return PKV_OK;
 }
 

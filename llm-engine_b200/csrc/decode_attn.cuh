@@ -46,6 +46,9 @@ struct DecodeArgs {
   float* part_ml;
   float* part_acc;
   int direct;  // 1: item i is token i over its whole history, no workspace
+  // shared-prefix units (decode_tma_kernel with TOK = 4 only): three int4 per unit
+  const int4* shared_items;
+  int n_shared;
 };
 
 constexpr int kDecodeThreads = 128;

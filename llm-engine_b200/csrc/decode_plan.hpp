@@ -49,6 +49,17 @@ struct WorkItem {
   int part;  // partial slot to write, or -1 to write the final output directly
 };
 
+// A unit of the shared-prefix planner: up to four tokens whose sequences have the same blocks
+// over keys [kv_begin, kv_begin + kv_len); each token's partial goes to its own slot.  Stored
+// behind the ordinary items in the same workspace region, three 16-byte slots each.
+struct SharedItem {
+  int kv_begin, kv_len, n_tok, pad;
+  int token[4];
+  int part[4];
+};
+static_assert(sizeof(SharedItem) == 3 * sizeof(WorkItem), "three item slots");
+constexpr int kSharedTokens = 4;
+
 struct TokSplit {
   int part_base;  // first partial slot of this token (valid when nsplits > 1)
   int nsplits;

@@ -52,11 +52,19 @@ template <int D, int MT, int NSTAGES, int WARPS> struct TmaSmem {
   static constexpr int kBytes = WARPS * kWarpBytes + 1024;
 };
 
-template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS>
+// TOK = 1: a unit serves one token.  TOK = 4: a unit serves up to four tokens whose sequences
+// share the blocks of its key range (a common prompt prefix): the K/V slab is fetched once and
+// the tokens' heads sit side by side in the N dimension (NT / TOK head tiles per token); every
+// token gets its own split-K partial.  Such units come from the shared-prefix planner as
+// SharedItem records (decode_plan.hpp).
+template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS, int TOK = 1>
 __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     decode_tma_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap kmap,
                       const __grid_constant__ CUtensorMap vmap) {
   using S = TmaSmem<D, MT, NSTAGES, WARPS>;
+  static_assert(TOK == 1 || TOK == 4, "a shared unit holds four tokens");
+  static_assert(NT % TOK == 0, "whole head tiles per token");
+  constexpr int NTG = NT / TOK;   // head tiles (8 heads each) per token
   constexpr int KS = D / 16;
   constexpr int HALVES = S::kHalves;
   constexpr int SLAB = 16 * MT;
@@ -89,7 +97,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   // plan, the workspace the previous merge has finished with).
   pdl_launch_dependents();
   pdl_wait();
-  const int n_items = a.direct ? a.n_tokens : a.header->n_items;
+  const int n_items = TOK > 1 ? a.n_shared : (a.direct ? a.n_tokens : a.header->n_items);
   const int total = n_items * a.kv_heads;
   const int gw = blockIdx.x * WARPS + warp, GW = gridDim.x * WARPS;
 
@@ -107,16 +115,26 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
       if (iu >= total) { iu = total; return false; }
       const int item = iu / a.kv_heads, kvh = iu - item * a.kv_heads;
       int token, part;
-      load_item(a, item, token, i_kvbeg, i_len, part);
+      if constexpr (TOK > 1) {
+        const int4 h0 = __ldg(a.shared_items + 3 * item), tk = __ldg(a.shared_items + 3 * item + 1);
+        i_kvbeg = h0.x;
+        i_len = h0.y;
+        token = tk.x;          // every token of the unit has the same blocks over this range
+        part = 0;
+      } else {
+        load_item(a, item, token, i_kvbeg, i_len, part);
+      }
       i_tbl = a.block_tables + __ldg(a.table_offset + __ldg(a.token_seq + token));
       i_nslabs = (i_len + SLAB - 1) / SLAB;
       i_slab = 0;
       i_x0 = kvh * D;
       i_ent_base = -64;
       // warm the query rows of this unit for the math side (group x D 16-bit values)
-      const char* qrow = reinterpret_cast<const char*>(static_cast<const T*>(a.q) +
-                                                       (static_cast<size_t>(token) * a.q_heads + kvh * a.group) * D);
-      if (lane * 128 < a.group * D * 2) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(qrow + lane * 128));
+      if constexpr (TOK == 1) {
+        const char* qrow = reinterpret_cast<const char*>(static_cast<const T*>(a.q) +
+                                                         (static_cast<size_t>(token) * a.q_heads + kvh * a.group) * D);
+        if (lane * 128 < a.group * D * 2) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(qrow + lane * 128));
+      }
     }
     const int box0 = i_slab * MT;
     if (box0 + MT > i_ent_base + 32) {   // fetch the entries of the next 32 boxes in one coalesced load
@@ -165,7 +183,18 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   for (int cu = gw; cu < total; cu += GW) {
     const int item = cu / a.kv_heads, kvh = cu - item * a.kv_heads;
     int token, kv_begin, kv_len, part;
-    load_item(a, item, token, kv_begin, kv_len, part);
+    int toks[TOK], parts[TOK], n_tok = 1;
+    if constexpr (TOK > 1) {
+      const int4 h0 = __ldg(a.shared_items + 3 * item), tk = __ldg(a.shared_items + 3 * item + 1),
+                 pt = __ldg(a.shared_items + 3 * item + 2);
+      kv_begin = h0.x; kv_len = h0.y; n_tok = h0.z;
+      toks[0] = tk.x; toks[1] = tk.y; toks[2] = tk.z; toks[3] = tk.w;
+      parts[0] = pt.x; parts[1] = pt.y; parts[2] = pt.z; parts[3] = pt.w;
+      token = toks[0]; part = parts[0];
+    } else {
+      load_item(a, item, token, kv_begin, kv_len, part);
+      toks[0] = token; parts[0] = part;
+    }
     const int n_slabs = (kv_len + SLAB - 1) / SLAB;
 
     while (more && n_issued - n_consumed < NSTAGES) more = issue_next();
@@ -173,11 +202,12 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     // Q^T fragments (B operand): rows = dims, columns = heads of the group.
     uint32_t qb[KS][NT][2];
     {
-      const T* qbase = static_cast<const T*>(a.q) + (static_cast<size_t>(token) * a.q_heads + kvh * a.group) * D;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int head = 8 * nt + g;
-        const bool hv = head < a.group;
+        const int ti = nt / NTG;                    // which token of the unit this head tile belongs to
+        const T* qbase = static_cast<const T*>(a.q) + (static_cast<size_t>(toks[ti]) * a.q_heads + kvh * a.group) * D;
+        const int head = 8 * (nt % NTG) + g;
+        const bool hv = head < a.group && ti < n_tok;
         const uint32_t* qrow = reinterpret_cast<const uint32_t*>(qbase + static_cast<size_t>(head) * D);
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
@@ -322,7 +352,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
       }
     }
     const int head_base = kvh * a.group;
-    if (part < 0) {
+    if (TOK == 1 && part < 0) {
       T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.q_heads + head_base) * D;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -342,11 +372,13 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
         }
       }
     } else {
-      float* pacc = a.part_acc + (static_cast<size_t>(part) * a.q_heads + head_base) * D;
-      float* pml = a.part_ml + (static_cast<size_t>(part) * a.q_heads + head_base) * 2;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int h0 = 8 * nt + 2 * c;
+        const int ti = nt / NTG;
+        if (ti >= n_tok) continue;
+        float* pacc = a.part_acc + (static_cast<size_t>(parts[ti]) * a.q_heads + head_base) * D;
+        float* pml = a.part_ml + (static_cast<size_t>(parts[ti]) * a.q_heads + head_base) * 2;
+        const int h0 = 8 * (nt % NTG) + 2 * c;
 #pragma unroll
         for (int dm = 0; dm < KS; ++dm) {
           const int d = 16 * dm + g;

@@ -113,6 +113,28 @@ class DecodePlan:
         _lib.check("pkv_decode_plan_host", st)
         return self
 
+    def build_host_shared(self, idx, block_size: int, min_saved_bytes: int = -1, stream=None) -> "DecodePlan":
+        """Shared-prefix-aware plan from the host copies of the step's index arrays (`idx`: a
+        StepIndices as returned by pack_step): sequences whose tables start with the same blocks
+        have that range read once per group of up to four tokens, if that saves at least
+        min_saved_bytes of K/V reads per layer (-1: the library's default; 0: always)."""
+        import numpy as np
+        pos = np.ascontiguousarray(idx.token_pos, dtype=np.int32)
+        seq = np.ascontiguousarray(idx.token_seq, dtype=np.int32)
+        tabs = np.ascontiguousarray(idx.block_tables, dtype=np.int32)
+        off = np.ascontiguousarray(idx.table_offset, dtype=np.int32)
+        p, n = self._ws()
+        st = _lib.lib().pkv_decode_plan_host_shared(pos.ctypes.data, seq.ctypes.data, tabs.ctypes.data, off.ctypes.data,
+                                                    self.n_tokens, off.size, tabs.size, block_size, self.q_heads,
+                                                    self.kv_heads, self.head_dim, min_saved_bytes, self.staging.data_ptr(),
+                                                    self.staging.numel(), p, n, _stream(stream), C.byref(self.plan))
+        _lib.check("pkv_decode_plan_host_shared", st)
+        return self
+
+    @property
+    def n_shared_units(self) -> int:
+        return int(self.plan.reserved) >> 1
+
     def build_device(self, token_pos, stream=None) -> "DecodePlan":
         p, n = self._ws()
         st = _lib.lib().pkv_decode_plan_device(_ptr(token_pos), self.n_tokens, self.q_heads, self.kv_heads,

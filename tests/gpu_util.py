@@ -54,7 +54,9 @@ def rel_errors(got, want):
 class Case:
     """One packed step over a fragmented pool."""
 
-    def __init__(self, orc, dtype, q_heads, kv_heads, head_dim, bs, num_blocks, seq_ctx, seq_new, seed, pkv):
+    def __init__(self, orc, dtype, q_heads, kv_heads, head_dim, bs, num_blocks, seq_ctx, seq_new, seed, pkv, share=None):
+        """share: [(member sequence indices, n_blocks)]: the members' first n_blocks table entries are
+        made those of the first member (a common prompt prefix held once in the pool)."""
         rng = np.random.default_rng(seed)
         self.dtype, self.qh, self.kvh, self.hd, self.bs, self.nb = dtype, q_heads, kv_heads, head_dim, bs, num_blocks
         kv_dim = kv_heads * head_dim
@@ -65,6 +67,10 @@ class Case:
             assert at + k <= num_blocks
             self.tables.append(perm[at:at + k].copy())
             at += k
+        for members, n_shared in (share or []):
+            for s in members[1:]:
+                assert n_shared * bs <= seq_ctx[s] and n_shared * bs <= seq_ctx[members[0]]   # new tokens land in private blocks
+                self.tables[s][:n_shared] = self.tables[members[0]][:n_shared]
         tok_tabs, tok_pos = [], []
         for s, (c, n) in enumerate(zip(seq_ctx, seq_new)):
             for i in range(n):
@@ -101,7 +107,7 @@ class Case:
         return d
 
     def run_gpu(self, pkv, torch, mode="split", d=None):
-        """mode: direct | split | host_plan | device_plan.  Returns (k_cache bits, v_cache bits, out fp32, dev dict)."""
+        """mode: direct | split | host_plan | shared_plan | device_plan.  Returns (k_cache bits, v_cache bits, out fp32, dev dict)."""
         d = d or self.upload(torch)
         kv_dim = self.kvh * self.hd
         pkv.launch_store_kv(d["k"], d["v"], d["slots"], d["kc"], d["vc"], self.N, kv_dim)
@@ -115,6 +121,8 @@ class Case:
             plan = pkv.DecodePlan(self.N, self.qh, self.kvh, self.hd)
             if mode == "host_plan":
                 plan.build_host(self.idx.token_pos)
+            elif mode == "shared_plan":
+                plan.build_host_shared(self.idx, self.bs, min_saved_bytes=0)
             else:
                 plan.build_device(d["token_pos"])
             plan.attention(*args, self.bs, self.scale)
