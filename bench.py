@@ -618,6 +618,109 @@ def compare_shared_plan(pkv, torch, dev, tables, positions, qh, kvh, hd, bs, nb,
     return res
 
 
+def run_head_sharded(args, rank, local_rank, world):
+    """--sharding head (cfg3, 2 or 4 GPUs): ONE batch for the whole job; rank r keeps the pools and the
+    query columns of kv heads [r*kvh/world, (r+1)*kvh/world) and computes them for all 256 sequences,
+    and every rank ends each layer with the full attention output.  Strong scaling.  --exchange peer
+    (default): the exchange is fused into the merge kernel (peer stores over NVLink + bounded flag
+    wait); --exchange nccl: local output, then an NCCL all-gather, for comparison."""
+    import torch
+    import torch.distributed as dist
+    pkv = importlib.import_module("llm-engine_b200")
+    wl = importlib.import_module("llm-engine_b200.workloads")
+    sh = importlib.import_module("llm-engine_b200.sharding")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    w = wl.make(args.workload, layers=args.layers)
+    if w.kv_heads % world:
+        raise SystemExit(f"--sharding head: {w.kv_heads} kv heads do not divide over {world} GPUs")
+    tdt = {"bf16": torch.bfloat16, "f16": torch.float16}[w.dtype]
+    bs, L, hd = w.block_size, w.layers, w.head_dim
+    q0, ql, kv0, kvl = sh.head_slices(w.q_heads, w.kv_heads, world, rank)
+    kv_dim_l, H_l, H = kvl * hd, ql * hd, w.q_heads * hd
+    tabs, pos, _ = w.step_tokens()
+    idx = pkv.pack_step(tabs, pos, bs)
+    N = idx.n_tokens
+    slots_total = w.num_blocks * bs
+    g = torch.Generator(device=dev).manual_seed(77 + rank)
+    pools = torch.empty((L, 2, slots_total, kv_dim_l), dtype=tdt, device=dev)
+    for l in range(L):
+        for j in range(2):
+            pools[l, j].copy_(torch.randn((slots_total, kv_dim_l), generator=g, device=dev, dtype=torch.float32))
+    q = torch.randn((L, N, H_l), generator=g, device=dev, dtype=torch.float32).to(tdt)
+    k = torch.randn((L, N, kv_dim_l), generator=g, device=dev, dtype=torch.float32).to(tdt)
+    v = torch.randn((L, N, kv_dim_l), generator=g, device=dev, dtype=torch.float32).to(tdt)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+    d_slots, d_seq, d_pos = i32(idx.slots), i32(idx.token_seq), i32(idx.token_pos)
+    d_tab, d_off = i32(idx.block_tables), i32(idx.table_offset)
+    plan = pkv.DecodePlan(N, ql, kvl, hd, device=dev)
+    ex = sh.HeadShardedExchange(N, w.q_heads, hd, tdt, dist, dev)
+    out_local = torch.zeros((N, H_l), dtype=tdt, device=dev)
+    out_full = torch.zeros((world, N, H_l), dtype=tdt, device=dev)
+
+    def step():
+        plan.build_host(idx.token_pos)
+        for l in range(L):
+            pkv.launch_store_kv(k[l], v[l], d_slots, pools[l, 0], pools[l, 1], N, kv_dim_l)
+            if args.exchange == "peer":
+                ex.attention(plan, q[l], pools[l, 0], pools[l, 1], d_tab, d_off, d_seq, d_pos, bs, w.scale)
+            else:
+                plan.attention(q[l], pools[l, 0], pools[l, 1], d_tab, d_off, d_seq, d_pos, out_local, bs, w.scale)
+                dist.all_gather_into_tensor(out_full, out_local)
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    # agreement of the two exchanges on the last layer (rank-major columns in the all-gather buffer)
+    if args.exchange == "peer":
+        plan.attention(q[L - 1], pools[L - 1, 0], pools[L - 1, 1], d_tab, d_off, d_seq, d_pos, out_local, bs, w.scale)
+        dist.all_gather_into_tensor(out_full, out_local)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(out_full.permute(1, 0, 2).reshape(N, H).view(torch.int16), ex.out.view(torch.int16)))
+    else:
+        same = None
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = torch.tensor([a.elapsed_time(b) / args.steps], dtype=torch.float64, device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms.item())
+    flags = pkv.debug_device_flags()
+    peak, src = peaks()
+    byts = w.decode_bytes_per_layer() / world            # this rank's share of the K/V bytes of a layer
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode tok/s (K/V append + paged decode attention over all layers)", "value": N / (ms_step * 1e-3),
+            "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {WORKLOAD_TEXT[args.workload]}", "layers": L,
+                       "sharding": f"by head: each rank holds {kvl} of {w.kv_heads} kv heads for all {N} sequences; every rank "
+                                   f"ends each layer with the full output",
+                       "exchange": "fused into the merge kernel: peer stores over NVLink + bounded flag wait" if args.exchange == "peer"
+                                   else "NCCL all-gather after the local attention",
+                       "launch": "eager launches"},
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_combine_kernel (+ exchange), whole step",
+                         "achieved": byts * L / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": byts * L / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src},
+            "exchange_bytes_per_layer_per_gpu": N * H_l * 2 * (world - 1), "peer_result_equals_nccl_result": same,
+            "device_error_flags": flags, "cpu_baseline": None, "e2e": None, "gpu_launches": 3 * L * args.steps, "clocks": clocks}), flush=True)
+    ex.close()
+    dist.destroy_process_group()
+
+
 def run_prefix_cow(args, rank, local_rank, world):
     """--workload cfg5: 128 sequences forked from one parent that holds a 512-token prefix plus a partial
     block; the first divergent write of each child triggers a copy-on-write block copy on every pool
@@ -758,6 +861,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--sharding", choices=("sequence", "head"), default="sequence",
+                    help="multi-GPU: independent batches per GPU (default, weak scaling) or one batch split by kv head")
+    ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer", help="--sharding head: how the output slices are exchanged")
     ap.add_argument("--host-pack", action="store_true", help="cfg5: build the step indices on the host instead of on the device")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling runs only; noted in config)")
@@ -772,7 +878,9 @@ def main():
     if world != args.gpus:
         if args.gpus > 1 and world == 1:
             raise SystemExit("--gpus N > 1 is launched with torch.distributed.run --nproc-per-node N")
-    if args.workload == "cfg4":
+    if args.sharding == "head" and world > 1 and args.workload in ("cfg2", "cfg3"):
+        run_head_sharded(args, rank, local_rank, world)
+    elif args.workload == "cfg4":
         run_prefill(args, rank, local_rank, world)
     elif args.workload == "cfg5":
         run_prefix_cow(args, rank, local_rank, world)

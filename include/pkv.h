@@ -56,7 +56,8 @@ const char* pkv_last_error(void);
 /* Debugging aid, the one entry point that SYNCHRONISES the device: reads and clears
  * the word in which kernels record a bounded wait that ran out (bit 0: a TMA
  * producer never saw its ring slot released; bit 1: a consumer never saw its tile
- * arrive; bit 2: a prefill pipeline wait).  0 means no kernel ever gave up.
+ * arrive; bit 2: a prefill pipeline wait; bit 3: a peer GPU's flag in the
+ * head-sharded exchange).  0 means no kernel ever gave up.
  * No llm-engine counterpart. */
 int pkv_debug_device_flags(unsigned int* flags);
 
@@ -215,6 +216,46 @@ int pkv_decode_attn_planned_f32(const pkv_decode_plan* plan, const void* q, cons
                                 const void* v_cache, const int* block_tables, const int* table_offset,
                                 const int* token_seq, const int* token_pos, void* out, int block_size,
                                 float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+
+/* ------------------------------------------------------------------ e -----
+ * Head-sharded decode over the GPUs of one box (one process per GPU).  The path
+ * scales by sequence without any exchange, and that is what the benchmark reports;
+ * this variant is for a configuration whose kv heads divide the GPU count and
+ * whose caller shards heads (tensor parallelism): rank r holds the pools of kv
+ * heads [r*kv_heads, (r+1)*kv_heads) only, computes q_heads local query heads for
+ * ALL tokens, and every rank needs the full [n_tokens][q_heads_total*head_dim]
+ * output.  No llm-engine counterpart (single GPU, src/model/cuda/cuda_model.cu:239).
+ *
+ * pkv_decode_attn_planned_peer_* is pkv_decode_attn_planned_* with the exchange
+ * fused into its merge kernel: each finished output row is stored straight into
+ * every rank's full buffer over NVLink (plain peer stores, 8 bytes each), then the
+ * rank raises flag `my_rank` on every peer and waits, with a bound, until its own
+ * n_peers flags show `epoch`; when the call's kernels have completed on the stream
+ * the whole output is in peer_out[my_rank].  peer_out / peer_flags are HOST arrays
+ * of n_peers device pointers as seen from this GPU (own buffer at index my_rank;
+ * flags are n_peers ints per rank, zero-initialised); epoch must grow by one per
+ * call (the same on every rank); plan->q_heads is the local head count.  A wait
+ * that runs out sets bit 3 of pkv_debug_device_flags and the kernel returns.
+ *
+ * pkv_peer_alloc / open / close / free are the set-up helpers for such buffers
+ * (cudaMalloc + CUDA IPC): the only entry points of the library that allocate or
+ * map device memory; call them before the serving loop. */
+int pkv_decode_attn_planned_peer_f16(const pkv_decode_plan* plan, const void* q, const void* k_cache,
+                                     const void* v_cache, const int* block_tables, const int* table_offset,
+                                     const int* token_seq, const int* token_pos, void* const* peer_out,
+                                     int* const* peer_flags, int n_peers, int my_rank, int epoch,
+                                     int q_heads_total, int block_size, float scale, void* workspace,
+                                     size_t workspace_bytes, pkv_stream stream);
+int pkv_decode_attn_planned_peer_bf16(const pkv_decode_plan* plan, const void* q, const void* k_cache,
+                                      const void* v_cache, const int* block_tables, const int* table_offset,
+                                      const int* token_seq, const int* token_pos, void* const* peer_out,
+                                      int* const* peer_flags, int n_peers, int my_rank, int epoch,
+                                      int q_heads_total, int block_size, float scale, void* workspace,
+                                      size_t workspace_bytes, pkv_stream stream);
+int pkv_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int pkv_peer_open(const void* handle64, void** ptr);
+int pkv_peer_close(void* ptr);
+int pkv_peer_free(void* ptr);
 
 /* ------------------------------------------------------------------ a3 ----
  * Paged (chunked) prefill attention on the tensor cores.  llm-engine has no such

@@ -43,6 +43,12 @@ SIGNATURES = {
     "pkv_decode_plan_staging_bytes": (_sz, [_i, _i]),
     "pkv_decode_plan_host": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
     "pkv_decode_plan_device": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
+    **{f"pkv_decode_attn_planned_peer_{s}": (_i, [C.POINTER(DecodePlan)] + [_vp] * 7 + [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp])
+       for s in ("f16", "bf16")},
+    "pkv_peer_alloc": (_i, [_sz, _vp, _vp]),
+    "pkv_peer_open": (_i, [_vp, _vp]),
+    "pkv_peer_close": (_i, [_vp]),
+    "pkv_peer_free": (_i, [_vp]),
     "pkv_decode_plan_host_shared": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, C.c_longlong, _vp, _sz, _vp, _sz, _vp,
                                          C.POINTER(DecodePlan)]),
     **{f"pkv_decode_attn_planned_{s}": (_i, [C.POINTER(DecodePlan)] + [_vp] * 8 + [_i, _f, _vp, _sz, _vp])

@@ -23,6 +23,7 @@ SOURCES = [
     "copy_blocks.cu",
     "rope_append.cu",
     "step_pack.cu",
+    "peer_memory.cu",
     "decode_attn.cu",
     "prefill_attn.cu",
     "engine_shim.cu",

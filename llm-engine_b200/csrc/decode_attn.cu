@@ -300,7 +300,7 @@ int launch_decode(const DecodeArgs& a, int grid, cudaStream_t stream, bool has_s
     }
   }
   const int st = launch_decode_main<T>(a, grid, stream, &log2_domain);
-  if (st != PKV_OK || !has_splits) return st;
+  if (st != PKV_OK || (!has_splits && a.n_peers == 0)) return st;   // with peers the merge kernel also does the exchange
   return log2_domain ? launch_combine<T, true>(a, stream) : launch_combine<T, false>(a, stream);
 }
 
@@ -347,6 +347,10 @@ void fill_args(DecodeArgs& a, const void* q, const void* kc, const void* vc, con
   a.direct = 1;
   a.shared_items = nullptr;
   a.n_shared = 0;
+  a.out_row_elems = static_cast<long long>(q_heads) * head_dim;
+  a.out_col0 = 0;
+  for (int p = 0; p < kMaxPeers; ++p) { a.peer_out[p] = nullptr; a.peer_flags[p] = nullptr; }
+  a.n_peers = 0; a.my_rank = 0; a.epoch = 0;
 }
 
 void attach_workspace(DecodeArgs& a, void* workspace, const WsLayout& w) {
@@ -403,11 +407,17 @@ int plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, i
   return PKV_OK;
 }
 
+struct PeerSetup {
+  void* const* out;      // host array: every rank's full output buffer (device pointers valid on this GPU)
+  int* const* flags;     // host array: every rank's flag array
+  int n_peers, my_rank, epoch, q_heads_total;
+};
+
 template <typename T>
 int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, const void* vc, const int* bt,
                    const int* to, const int* ts, const int* tp, void* out, int block_size, float scale,
-                   void* workspace, size_t workspace_bytes, pkv_stream stream) {
-  const char* fn = "pkv_decode_attn_planned";
+                   void* workspace, size_t workspace_bytes, pkv_stream stream, const PeerSetup* peers = nullptr) {
+  const char* fn = peers ? "pkv_decode_attn_planned_peer" : "pkv_decode_attn_planned";
   if (!plan) return fail(PKV_E_ARG, "%s: null plan", fn);
   if (plan->n_tokens <= 0) return PKV_OK;
   int st = validate_geometry(fn, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size);
@@ -421,6 +431,23 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
   DecodeArgs a;
   fill_args(a, q, kc, vc, bt, to, ts, tp, out, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size, scale);
   attach_workspace(a, workspace, w);
+  if (peers) {
+    if constexpr (sizeof(T) != 2) return fail(PKV_E_UNSUPPORTED, "%s: the head-sharded exchange is for 16-bit outputs", fn);
+    if (peers->n_peers < 1 || peers->n_peers > kMaxPeers || peers->my_rank < 0 || peers->my_rank >= peers->n_peers)
+      return fail(PKV_E_ARG, "%s: rank %d of %d (at most %d)", fn, peers->my_rank, peers->n_peers, kMaxPeers);
+    if (peers->q_heads_total != plan->q_heads * peers->n_peers || (plan->head_dim & 3))
+      return fail(PKV_E_ARG, "%s: %d heads in all must be %d ranks x %d local heads, head_dim a multiple of 4", fn,
+                  peers->q_heads_total, peers->n_peers, plan->q_heads);
+    for (int p = 0; p < peers->n_peers; ++p) {
+      if (!peers->out[p] || !peers->flags[p]) return fail(PKV_E_ARG, "%s: null peer pointer for rank %d", fn, p);
+      a.peer_out[p] = peers->out[p];
+      a.peer_flags[p] = peers->flags[p];
+    }
+    if (peers->out[peers->my_rank] != out) return fail(PKV_E_ARG, "%s: out must be this rank's own full buffer", fn);
+    a.n_peers = peers->n_peers; a.my_rank = peers->my_rank; a.epoch = peers->epoch;
+    a.out_row_elems = static_cast<long long>(peers->q_heads_total) * plan->head_dim;
+    a.out_col0 = peers->my_rank * plan->q_heads * plan->head_dim;
+  }
   const int n_shared = plan->reserved >> 1;
   if (n_shared > 0) {
     if (!shared_units_ok<T>(a))
@@ -807,5 +834,22 @@ int pkv_decode_attn_bf16_builtin_scratch(const void* q, const void* k_cache, con
 PKV_DECODE_ENTRY(f16, __half)
 PKV_DECODE_ENTRY(bf16, __nv_bfloat16)
 PKV_DECODE_ENTRY(f32, float)
+
+#define PKV_DECODE_PEER_ENTRY(SUFFIX, TYPE)                                                                          \
+  int pkv_decode_attn_planned_peer_##SUFFIX(const pkv_decode_plan* plan, const void* q, const void* k_cache,        \
+                                            const void* v_cache, const int* block_tables, const int* table_offset,  \
+                                            const int* token_seq, const int* token_pos, void* const* peer_out,      \
+                                            int* const* peer_flags, int n_peers, int my_rank, int epoch,            \
+                                            int q_heads_total, int block_size, float scale, void* workspace,        \
+                                            size_t workspace_bytes, pkv_stream stream) {                            \
+    if (!peer_out || !peer_flags || n_peers < 1 || my_rank < 0 || my_rank >= n_peers)                               \
+      return fail(PKV_E_ARG, "pkv_decode_attn_planned_peer: null peer arrays or rank %d of %d", my_rank, n_peers);  \
+    const PeerSetup ps{peer_out, peer_flags, n_peers, my_rank, epoch, q_heads_total};                               \
+    return decode_planned<TYPE>(plan, q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos,        \
+                                peer_out[my_rank], block_size, scale, workspace, workspace_bytes, stream, &ps);     \
+  }
+
+PKV_DECODE_PEER_ENTRY(f16, __half)
+PKV_DECODE_PEER_ENTRY(bf16, __nv_bfloat16)
 
 }  // extern "C"

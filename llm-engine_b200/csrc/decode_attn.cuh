@@ -26,6 +26,12 @@
 
 namespace pkv {
 
+// Word in which kernels record a bounded wait that ran out (read and cleared by pkv_debug_device_flags).
+__device__ unsigned int g_pkv_device_error = 0;
+
+constexpr int kMaxPeers = 8;
+constexpr unsigned kErrPeerWait = 8u;   // bit of the device error word: a peer's flag did not arrive in time
+
 struct DecodeArgs {
   const void* q;
   const void* k_cache;
@@ -49,7 +55,24 @@ struct DecodeArgs {
   // shared-prefix units (decode_tma_kernel with TOK = 4 only): three int4 per unit
   const int4* shared_items;
   int n_shared;
+  // Where a token's output row lives: out + token * out_row_elems + out_col0 + head * head_dim.
+  // (q_heads * head_dim and 0 unless the heads of a row are spread over several GPUs.)
+  long long out_row_elems;
+  int out_col0;
+  // Head-sharded exchange, done by the merge kernel (n_peers = 0: off).  peer_out[p] is rank p's
+  // full output buffer (this rank's own is peer_out[my_rank] == out), peer_flags[p] an array of
+  // n_peers ints on rank p; this rank writes `epoch` to peer_flags[p][my_rank] once all its rows
+  // have been stored everywhere, and waits until its own flags all show `epoch`.
+  void* peer_out[kMaxPeers];
+  int* peer_flags[kMaxPeers];
+  int n_peers, my_rank, epoch;
 };
+
+// Output row of (token, head 0) under the layout above.
+template <typename T>
+__device__ __forceinline__ T* out_row(const DecodeArgs& a, void* base, int token) {
+  return static_cast<T*>(base) + static_cast<size_t>(token) * a.out_row_elems + a.out_col0;
+}
 
 constexpr int kDecodeThreads = 128;
 constexpr int kDecodeWarps = 4;
@@ -109,7 +132,6 @@ __device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int t
     sm_w[(kDecodeWarps + 1) * 16 + tid] = l;
   }
   G::sync();
-  T* out = static_cast<T*>(a.out);
   for (int idx = tid; idx < rows * D; idx += G::size()) {
     const int r = idx / D, d = idx - r * D;
     float acc = 0.f;
@@ -118,7 +140,7 @@ __device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int t
     const int head = head0 + r;
     if (part < 0) {
       const float l = sm_w[(kDecodeWarps + 1) * 16 + r];
-      out[(static_cast<size_t>(token) * a.q_heads + head) * D + d] = Elem<T>::from_f32(acc / l);
+      out_row<T>(a, a.out, token)[static_cast<size_t>(head) * D + d] = Elem<T>::from_f32(acc / l);
     } else {
       a.part_acc[(static_cast<size_t>(part) * a.q_heads + head) * D + d] = acc;
     }
@@ -150,15 +172,51 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
   pdl_launch_dependents();
   pdl_wait();  // the attention kernel's partials
   const int D = a.head_dim;
-  T* out = static_cast<T*>(a.out);
   constexpr int B = kCombineBatch;
   const int pairs = a.n_tokens * a.kv_heads;
   for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
     const int token = pr / a.kv_heads, kvh = pr - token * a.kv_heads;
     const TokSplit ts = a.tok_split[token];
-    if (ts.nsplits <= 1) continue;
+    if (ts.nsplits <= 1 && a.n_peers == 0) continue;
     const int head0 = kvh * a.group;
-    if ((D & 3) == 0) {
+    if (a.n_peers > 0) {
+      // Head-sharded exchange (16-bit outputs, head_dim a multiple of 4): every row of this rank's
+      // heads goes to every rank's full output buffer, 8 bytes at a time over NVLink.
+      if constexpr (sizeof(T) == 2) {
+        const int D4 = D >> 2;
+        for (int idx = threadIdx.x; idx < a.group * D4; idx += kCombineThreads) {
+          const int r = idx / D4, d4 = idx - r * D4;
+          const int head = head0 + r;
+          const size_t off = static_cast<size_t>(head) * D + 4 * d4;
+          uint2 packed;
+          if (ts.nsplits <= 1) {
+            packed = *reinterpret_cast<const uint2*>(out_row<T>(a, a.out, token) + off);   // the attention kernel wrote it here
+          } else {
+            float m_run = -INFINITY, l_run = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < ts.nsplits; ++s) {
+              const size_t p = static_cast<size_t>(ts.part_base + s) * a.q_heads + head;
+              const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + p * 2));
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_acc + p * D) + d4);
+              const float mb = fmaxf(m_run, ml.x);
+              const float f0 = (m_run == -INFINITY) ? 0.f : softmax_exp<LOG2>(m_run - mb);
+              const float f = (ml.x == -INFINITY) ? 0.f : softmax_exp<LOG2>(ml.x - mb);
+              l_run = l_run * f0 + f * ml.y;
+              acc.x = acc.x * f0 + f * v.x; acc.y = acc.y * f0 + f * v.y;
+              acc.z = acc.z * f0 + f * v.z; acc.w = acc.w * f0 + f * v.w;
+              m_run = mb;
+            }
+            const float inv = 1.f / l_run;
+            packed.x = pack2<T>(acc.x * inv, acc.y * inv);
+            packed.y = pack2<T>(acc.z * inv, acc.w * inv);
+          }
+          for (int p = 0; p < a.n_peers; ++p) {
+            if (p == a.my_rank && ts.nsplits <= 1) continue;
+            *reinterpret_cast<uint2*>(out_row<T>(a, a.peer_out[p], token) + off) = packed;
+          }
+        }
+      }
+    } else if ((D & 3) == 0) {
       const int D4 = D >> 2;
       for (int idx = threadIdx.x; idx < a.group * D4; idx += kCombineThreads) {
         const int r = idx / D4, d4 = idx - r * D4;
@@ -194,7 +252,7 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
           m_run = mb;
         }
         const float inv = 1.f / l_run;
-        T* o = out + (static_cast<size_t>(token) * a.q_heads + head) * D + 4 * d4;
+        T* o = out_row<T>(a, a.out, token) + static_cast<size_t>(head) * D + 4 * d4;
         o[0] = Elem<T>::from_f32(acc.x * inv);
         o[1] = Elem<T>::from_f32(acc.y * inv);
         o[2] = Elem<T>::from_f32(acc.z * inv);
@@ -214,7 +272,38 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
           l += f * __ldcg(a.part_ml + p * 2 + 1);
           acc += f * __ldcg(a.part_acc + p * D + d);
         }
-        out[(static_cast<size_t>(token) * a.q_heads + head) * D + d] = Elem<T>::from_f32(acc / l);
+        out_row<T>(a, a.out, token)[static_cast<size_t>(head) * D + d] = Elem<T>::from_f32(acc / l);
+      }
+    }
+  }
+  if (a.n_peers > 0) {
+    // Tell every rank that this rank's rows are in its buffer, and leave only when every rank has
+    // told this one: the kernel's completion then means the full output is here.  Stores to the
+    // peers are made visible system-wide before the block counts itself done; the last block to do
+    // so raises the flags and waits, with a bound, for the others'.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int done = atomicAdd(a.counters, 1);
+      if (done == static_cast<int>(gridDim.x) - 1) {
+        a.counters[0] = 0;                                   // ready for the next launch
+        __threadfence_system();
+        for (int p = 0; p < a.n_peers; ++p)
+          asm volatile("st.release.sys.global.s32 [%0], %1;\n" ::"l"(a.peer_flags[p] + a.my_rank), "r"(a.epoch) : "memory");
+        const int* mine = a.peer_flags[a.my_rank];
+        for (int p = 0; p < a.n_peers; ++p) {
+          int seen = 0;
+          unsigned spins = 0;
+          for (;;) {
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];\n" : "=r"(seen) : "l"(mine + p) : "memory");
+            if (seen - a.epoch >= 0) break;
+            if (++spins > (1u << 23)) {                      // about two seconds: the peer is not coming
+              atomicOr(&g_pkv_device_error, kErrPeerWait);
+              break;
+            }
+            __nanosleep(200);
+          }
+        }
       }
     }
   }

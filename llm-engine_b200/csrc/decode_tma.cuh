@@ -33,7 +33,6 @@
 
 namespace pkv {
 
-__device__ unsigned int g_pkv_device_error = 0;
 constexpr unsigned kErrProducerWait = 1u, kErrConsumerWait = 2u;
 
 constexpr int kBoxBytes = 16 * 128;
@@ -353,7 +352,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     }
     const int head_base = kvh * a.group;
     if (TOK == 1 && part < 0) {
-      T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.q_heads + head_base) * D;
+      T* out = out_row<T>(a, a.out, token) + static_cast<size_t>(head_base) * D;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const int h0 = 8 * nt + 2 * c;

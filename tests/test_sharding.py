@@ -54,3 +54,18 @@ def test_two_rank_reduction_over_gloo(pkv, tmp_path):
     assert float(line[1]) == 32.0      # tokens summed over both ranks
     assert float(line[2]) == 15.0      # the slower rank's time
     assert int(line[3]) == 256         # every sequence of the shared batch owned exactly once
+
+
+def test_head_slices_partition_the_heads():
+    import importlib
+    sh = importlib.import_module("llm-engine_b200.sharding")
+    for qh, kvh, world in ((32, 4, 2), (32, 4, 4), (14, 2, 2), (8, 8, 8)):
+        seen_q, seen_kv = [], []
+        for r in range(world):
+            q0, ql, kv0, kvl = sh.head_slices(qh, kvh, world, r)
+            assert ql * kvh == qh * kvl                       # whole GQA groups
+            seen_q += list(range(q0, q0 + ql)); seen_kv += list(range(kv0, kv0 + kvl))
+        assert seen_q == list(range(qh)) and seen_kv == list(range(kvh))
+    import pytest
+    with pytest.raises(ValueError):
+        sh.head_slices(14, 2, 4, 0)
