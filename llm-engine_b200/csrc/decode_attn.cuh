@@ -167,12 +167,49 @@ __device__ __forceinline__ void merge_warps_and_store(const DecodeArgs& a, int t
 constexpr int kCombineThreads = 128;
 constexpr int kCombineBatch = 16;
 
+// Folds the partials of (token, head) for dims 4 d4 .. 4 d4 + 3 and returns the normalised values.
+template <bool LOG2>
+__device__ __forceinline__ float4 merge_partials4(const DecodeArgs& a, const TokSplit ts, int head, int d4, int D) {
+  constexpr int B = kCombineBatch;
+  float m_run = -INFINITY, l_run = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = 0; s0 < ts.nsplits; s0 += B) {
+    float2 ml[B];
+    float4 v[B];
+#pragma unroll
+    for (int i = 0; i < B; ++i) {
+      if (s0 + i < ts.nsplits) {
+        const size_t p = static_cast<size_t>(ts.part_base + s0 + i) * a.q_heads + head;
+        ml[i] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + p * 2));
+        v[i] = __ldcg(reinterpret_cast<const float4*>(a.part_acc + p * D) + d4);
+      } else {
+        ml[i] = make_float2(-INFINITY, 0.f);
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    float mb = m_run;
+#pragma unroll
+    for (int i = 0; i < B; ++i) mb = fmaxf(mb, ml[i].x);
+    const float f0 = (m_run == -INFINITY) ? 0.f : softmax_exp<LOG2>(m_run - mb);
+    l_run *= f0;
+    acc.x *= f0; acc.y *= f0; acc.z *= f0; acc.w *= f0;
+#pragma unroll
+    for (int i = 0; i < B; ++i) {
+      const float f = (ml[i].x == -INFINITY) ? 0.f : softmax_exp<LOG2>(ml[i].x - mb);
+      l_run += f * ml[i].y;
+      acc.x += f * v[i].x; acc.y += f * v[i].y; acc.z += f * v[i].z; acc.w += f * v[i].w;
+    }
+    m_run = mb;
+  }
+  const float inv = 1.f / l_run;
+  return make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
 template <typename T, bool LOG2>
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecodeArgs a) {
   pdl_launch_dependents();
   pdl_wait();  // the attention kernel's partials
   const int D = a.head_dim;
-  constexpr int B = kCombineBatch;
   const int pairs = a.n_tokens * a.kv_heads;
   for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
     const int token = pr / a.kv_heads, kvh = pr - token * a.kv_heads;
@@ -192,23 +229,9 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
           if (ts.nsplits <= 1) {
             packed = *reinterpret_cast<const uint2*>(out_row<T>(a, a.out, token) + off);   // the attention kernel wrote it here
           } else {
-            float m_run = -INFINITY, l_run = 0.f;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < ts.nsplits; ++s) {
-              const size_t p = static_cast<size_t>(ts.part_base + s) * a.q_heads + head;
-              const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + p * 2));
-              const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_acc + p * D) + d4);
-              const float mb = fmaxf(m_run, ml.x);
-              const float f0 = (m_run == -INFINITY) ? 0.f : softmax_exp<LOG2>(m_run - mb);
-              const float f = (ml.x == -INFINITY) ? 0.f : softmax_exp<LOG2>(ml.x - mb);
-              l_run = l_run * f0 + f * ml.y;
-              acc.x = acc.x * f0 + f * v.x; acc.y = acc.y * f0 + f * v.y;
-              acc.z = acc.z * f0 + f * v.z; acc.w = acc.w * f0 + f * v.w;
-              m_run = mb;
-            }
-            const float inv = 1.f / l_run;
-            packed.x = pack2<T>(acc.x * inv, acc.y * inv);
-            packed.y = pack2<T>(acc.z * inv, acc.w * inv);
+            const float4 r4 = merge_partials4<LOG2>(a, ts, head, d4, D);
+            packed.x = pack2<T>(r4.x, r4.y);
+            packed.y = pack2<T>(r4.z, r4.w);
           }
           for (int p = 0; p < a.n_peers; ++p) {
             if (p == a.my_rank && ts.nsplits <= 1) continue;
@@ -221,42 +244,12 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
       for (int idx = threadIdx.x; idx < a.group * D4; idx += kCombineThreads) {
         const int r = idx / D4, d4 = idx - r * D4;
         const int head = head0 + r;
-        float m_run = -INFINITY, l_run = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < ts.nsplits; s0 += B) {
-          float2 ml[B];
-          float4 v[B];
-#pragma unroll
-          for (int i = 0; i < B; ++i) {
-            if (s0 + i < ts.nsplits) {
-              const size_t p = static_cast<size_t>(ts.part_base + s0 + i) * a.q_heads + head;
-              ml[i] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + p * 2));
-              v[i] = __ldcg(reinterpret_cast<const float4*>(a.part_acc + p * D) + d4);
-            } else {
-              ml[i] = make_float2(-INFINITY, 0.f);
-              v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-          }
-          float mb = m_run;
-#pragma unroll
-          for (int i = 0; i < B; ++i) mb = fmaxf(mb, ml[i].x);
-          const float f0 = (m_run == -INFINITY) ? 0.f : softmax_exp<LOG2>(m_run - mb);
-          l_run *= f0;
-          acc.x *= f0; acc.y *= f0; acc.z *= f0; acc.w *= f0;
-#pragma unroll
-          for (int i = 0; i < B; ++i) {
-            const float f = (ml[i].x == -INFINITY) ? 0.f : softmax_exp<LOG2>(ml[i].x - mb);
-            l_run += f * ml[i].y;
-            acc.x += f * v[i].x; acc.y += f * v[i].y; acc.z += f * v[i].z; acc.w += f * v[i].w;
-          }
-          m_run = mb;
-        }
-        const float inv = 1.f / l_run;
+        const float4 r4 = merge_partials4<LOG2>(a, ts, head, d4, D);
         T* o = out_row<T>(a, a.out, token) + static_cast<size_t>(head) * D + 4 * d4;
-        o[0] = Elem<T>::from_f32(acc.x * inv);
-        o[1] = Elem<T>::from_f32(acc.y * inv);
-        o[2] = Elem<T>::from_f32(acc.z * inv);
-        o[3] = Elem<T>::from_f32(acc.w * inv);
+        o[0] = Elem<T>::from_f32(r4.x);
+        o[1] = Elem<T>::from_f32(r4.y);
+        o[2] = Elem<T>::from_f32(r4.z);
+        o[3] = Elem<T>::from_f32(r4.w);
       }
     } else {
       for (int idx = threadIdx.x; idx < a.group * D; idx += kCombineThreads) {

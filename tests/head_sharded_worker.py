@@ -27,7 +27,7 @@ def main():
     rng = np.random.default_rng(3)
     ctx = [int(x) for x in rng.integers(1, 3000, size=40)] + [5000, 17, 64]
     for dtype in ("bf16", "f16"):
-        case = Case(orc, dtype, qh, kvh, hd, bs, 2048, ctx, [1] * len(ctx), 4242, pkv)
+        case = Case(orc, dtype, qh, kvh, hd, bs, 8192, ctx, [1] * len(ctx), 4242, pkv)
         _, _, want = case.expected(orc)
         q0, ql, kv0, kvl = sharding.head_slices(qh, kvh, world, rank)
         cols = lambda a, h0, n: np.ascontiguousarray(a[:, h0 * hd:(h0 + n) * hd])
