@@ -677,6 +677,16 @@ def run_head_sharded(args, rank, local_rank, world):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    replay = step
+    if not args.no_graph:
+        plan.build_host(idx.token_pos)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        replay = graph.replay
+        for _ in range(3):
+            replay()
+        barrier()
     # agreement of the two exchanges on the last layer (rank-major columns in the all-gather buffer)
     if args.exchange == "peer":
         plan.attention(q[L - 1], pools[L - 1, 0], pools[L - 1, 1], d_tab, d_off, d_seq, d_pos, out_local, bs, w.scale)
@@ -691,7 +701,7 @@ def run_head_sharded(args, rank, local_rank, world):
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(args.steps):
-        step()
+        replay()
     b.record()
     barrier()
     clocks = sampler.stop()
@@ -711,7 +721,7 @@ def run_head_sharded(args, rank, local_rank, world):
                                    f"ends each layer with the full output",
                        "exchange": "fused into the merge kernel: peer stores over NVLink + bounded flag wait" if args.exchange == "peer"
                                    else "NCCL all-gather after the local attention",
-                       "launch": "eager launches"},
+                       "launch": "eager launches" if args.no_graph else "cuda graph replay"},
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_combine_kernel (+ exchange), whole step",
                          "achieved": byts * L / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": byts * L / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src},

@@ -233,8 +233,13 @@ int pkv_decode_attn_planned_f32(const pkv_decode_plan* plan, const void* q, cons
  * n_peers flags show `epoch`; when the call's kernels have completed on the stream
  * the whole output is in peer_out[my_rank].  peer_out / peer_flags are HOST arrays
  * of n_peers device pointers as seen from this GPU (own buffer at index my_rank;
- * flags are n_peers ints per rank, zero-initialised); epoch must grow by one per
- * call (the same on every rank); plan->q_heads is the local head count.  A wait
+ * flags are n_peers + 1 ints per rank, zero-initialised); epoch must grow by one
+ * per call, the same on every rank, or be 0: the calls are then counted on the
+ * device (in the extra int), which lets a captured CUDA graph be replayed;
+ * plan->q_heads is the local head count.  A rank may enter its next call while a
+ * peer still reads the output of this one, so a caller whose consumer is not already
+ * ordered before the peers' next call (tensor-parallel layers are, by the all-reduce
+ * that follows the output projection) alternates two buffers.  A wait
  * that runs out sets bit 3 of pkv_debug_device_flags and the kernel returns.
  *
  * pkv_peer_alloc / open / close / free are the set-up helpers for such buffers

@@ -280,16 +280,19 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
       const int done = atomicAdd(a.counters, 1);
       if (done == static_cast<int>(gridDim.x) - 1) {
         a.counters[0] = 0;                                   // ready for the next launch
+        int* mine = a.peer_flags[a.my_rank];
+        // epoch 0: count the calls on the device (slot n_peers of this rank's own flags), so that a
+        // captured CUDA graph can be replayed; every rank makes the same calls and counts alike.
+        const int epoch = a.epoch != 0 ? a.epoch : (mine[a.n_peers] += 1);
         __threadfence_system();
         for (int p = 0; p < a.n_peers; ++p)
-          asm volatile("st.release.sys.global.s32 [%0], %1;\n" ::"l"(a.peer_flags[p] + a.my_rank), "r"(a.epoch) : "memory");
-        const int* mine = a.peer_flags[a.my_rank];
+          asm volatile("st.release.sys.global.s32 [%0], %1;\n" ::"l"(a.peer_flags[p] + a.my_rank), "r"(epoch) : "memory");
         for (int p = 0; p < a.n_peers; ++p) {
           int seen = 0;
           unsigned spins = 0;
           for (;;) {
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];\n" : "=r"(seen) : "l"(mine + p) : "memory");
-            if (seen - a.epoch >= 0) break;
+            if (seen - epoch >= 0) break;
             if (++spins > (1u << 23)) {                      // about two seconds: the peer is not coming
               atomicOr(&g_pkv_device_error, kErrPeerWait);
               break;

@@ -103,16 +103,17 @@ class HeadShardedExchange:
         self._flag_arr = (C.c_void_p * self.world)(*[p + self.flag_off for p in self._ptrs])
         raw = torch.as_tensor(_RawCuda(self._own, total), device=device)
         self.out = raw[:self.out_bytes].view(torch_dtype).view(n_tokens, q_heads_total * head_dim)
-        self.flags = raw[self.flag_off:self.flag_off + 4 * self.world].view(torch.int32)
+        self.flags = raw[self.flag_off:self.flag_off + 4 * (self.world + 1)].view(torch.int32)
         self.epoch = 0
         dist.barrier()
 
     def attention(self, plan, q_local, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos,
-                  block_size: int, scale: float, stream=None):
+                  block_size: int, scale: float, stream=None, device_epoch: bool = True):
         """plan: a DecodePlan built for the LOCAL head counts.  Returns this rank's full output
-        (valid once the stream has run the call)."""
+        (valid once the stream has run the call).  device_epoch: the calls are counted on the device
+        (replayable in a CUDA graph); otherwise the host passes a growing epoch."""
         from .kernels import _ptr, _stream, _suffix
-        self.epoch += 1
+        self.epoch = 0 if device_epoch else self.epoch + 1
         fn = f"pkv_decode_attn_planned_peer_{_suffix(k_cache)}"
         p, n = plan._ws()
         st = getattr(self._lib.lib(), fn)(self.C.byref(plan.plan), _ptr(q_local), _ptr(k_cache), _ptr(v_cache),
