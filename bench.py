@@ -727,8 +727,17 @@ def run_head_sharded(args, rank, local_rank, world):
                          "frac": byts * L / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src},
             "exchange_bytes_per_layer_per_gpu": N * H_l * 2 * (world - 1), "peer_result_equals_nccl_result": same,
             "device_error_flags": flags, "cpu_baseline": None, "e2e": None, "gpu_launches": 3 * L * args.steps, "clocks": clocks}), flush=True)
+    # Tear-down: the captured graph (it holds NCCL kernels in --exchange nccl) goes first; a watchdog
+    # ends the process if a collective's tear-down does not return.
+    sys.stdout.flush()
+    threading.Timer(20.0, lambda: os._exit(0)).start()
+    replay = None
+    if not args.no_graph:
+        del graph
+    torch.cuda.synchronize()
     ex.close()
     dist.destroy_process_group()
+    os._exit(0)
 
 
 def run_prefix_cow(args, rank, local_rank, world):
