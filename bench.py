@@ -239,13 +239,23 @@ def run_ours(args, rank, local_rank, world):
     kc_l, vc_l = [pools[l, 0] for l in range(L)], [pools[l, 1] for l in range(L)]
     q_l, k_l, v_l, out_l = [q[l] for l in range(L)], [k[l] for l in range(L)], [v[l] for l in range(L)], [out[l] for l in range(L)]
 
+    # Decode steps on the TMA kernel take the append inside the attention launch (one kernel per layer
+    # fewer); --separate-append keeps the reference's two calls per layer.
+    fused = w.dtype != "f32" and not args.separate_append
+
+    def layer(l, qq, kk, vv, oo):
+        if fused:
+            plan.append_attention(qq, kk, vv, d_slots, kc_l[l], vc_l[l], d_tab, d_off, d_seq, d_pos, oo, bs, w.scale)
+        else:
+            pkv.launch_store_kv(kk, vv, d_slots, kc_l[l], vc_l[l], N, kv_dim)
+            plan.attention(qq, kc_l[l], vc_l[l], d_tab, d_off, d_seq, d_pos, oo, bs, w.scale)
+
     def step_resident():
         plan.build_host(idx.token_pos)
         for l in range(L):
-            pkv.launch_store_kv(k_l[l], v_l[l], d_slots, kc_l[l], vc_l[l], N, kv_dim)
-            plan.attention(q_l[l], kc_l[l], vc_l[l], d_tab, d_off, d_seq, d_pos, out_l[l], bs, w.scale)
+            layer(l, q_l[l], k_l[l], v_l[l], out_l[l])
 
-    launches_per_step = 2 * L
+    launches_per_step = (2 if fused else 3) * L      # kernels: [append,] attention, merge
 
     # ---- end-to-end step: host buffers in, host buffers out --------------------------
     pin = lambda t: t.cpu().pin_memory()
@@ -280,8 +290,7 @@ def run_ours(args, rank, local_rank, world):
                 up_done.append(ev)
         for l in range(L):
             main.wait_event(up_done[l])
-            pkv.launch_store_kv(e_k[l], e_v[l], d_slots, kc_l[l], vc_l[l], N, kv_dim)
-            plan.attention(e_q[l], kc_l[l], vc_l[l], d_tab, d_off, d_seq, d_pos, e_out[l], bs, w.scale)
+            layer(l, e_q[l], e_k[l], e_v[l], e_out[l])
             ev = torch.cuda.Event()
             ev.record(main)
             out_stream.wait_event(ev)
@@ -359,10 +368,14 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.synchronize()
     for _ in range(args.steps):
         for l in range(L):
-            pkv.launch_store_kv(k_l[l], v_l[l], d_slots, kc_l[l], vc_l[l], N, kv_dim)
+            if not fused:
+                pkv.launch_store_kv(k_l[l], v_l[l], d_slots, kc_l[l], vc_l[l], N, kv_dim)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            plan.attention(q_l[l], kc_l[l], vc_l[l], d_tab, d_off, d_seq, d_pos, out_l[l], bs, w.scale)
+            if fused:
+                plan.append_attention(q_l[l], k_l[l], v_l[l], d_slots, kc_l[l], vc_l[l], d_tab, d_off, d_seq, d_pos, out_l[l], bs, w.scale)
+            else:
+                plan.attention(q_l[l], kc_l[l], vc_l[l], d_tab, d_off, d_seq, d_pos, out_l[l], bs, w.scale)
             b.record()
             evs.append((a, b))
     torch.cuda.synchronize()
@@ -411,6 +424,7 @@ def run_ours(args, rank, local_rank, world):
                        "layers": L, "sharding": "by sequence: each rank owns its pool and its batch, no collective",
                        "l2": f"per-step working set {algo_bytes * L / 1e9:.2f} GB across {L} distinct per-layer pools, far larger than the 126 MB L2",
                        "launch": "cuda graph replay" if use_graph else "eager launches",
+                       "append": "inside the attention launch (pkv_append_decode_attn_planned)" if fused else "separate launch (pkv_append)",
                        **({"layers_override": args.layers} if args.layers else {})},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
@@ -880,6 +894,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--separate-append", action="store_true", help="decode: K/V append as its own launch, as the reference calls it")
     ap.add_argument("--sharding", choices=("sequence", "head"), default="sequence",
                     help="multi-GPU: independent batches per GPU (default, weak scaling) or one batch split by kv head")
     ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer", help="--sharding head: how the output slices are exchanged")

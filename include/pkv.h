@@ -182,6 +182,27 @@ int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int 
 int pkv_decode_plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
                            void* workspace, size_t workspace_bytes, pkv_stream stream,
                            pkv_decode_plan* plan);
+/* Append fused into the attention: pkv_append_* followed by pkv_decode_attn_planned_*
+ * in ONE kernel chain less (the two calls of src/model/cuda/cuda_model.cu:368-377
+ * folded together).  The work unit that reaches a token's newest key takes that
+ * key's K/V row from k / v instead of the pool and writes it to pool row
+ * slots[token]; the pools end up byte-identical to what pkv_append_* writes.  For
+ * decode steps only: every sequence brings exactly one token (a sequence that
+ * brings several needs its earlier new keys in the pool first: append, then
+ * pkv_decode_attn_planned_*).  Runs where the TMA kernel runs (16-bit K/V, head_dim
+ * 64 or 128, at most 16 query heads per kv head, block_size a power of two >= 16);
+ * PKV_E_UNSUPPORTED otherwise, with nothing enqueued. */
+int pkv_append_decode_attn_planned_f16(const pkv_decode_plan* plan, const void* q, const void* k, const void* v,
+                                       const int* slots, void* k_cache, void* v_cache, const int* block_tables,
+                                       const int* table_offset, const int* token_seq, const int* token_pos,
+                                       void* out, int block_size, float scale, void* workspace,
+                                       size_t workspace_bytes, pkv_stream stream);
+int pkv_append_decode_attn_planned_bf16(const pkv_decode_plan* plan, const void* q, const void* k, const void* v,
+                                        const int* slots, void* k_cache, void* v_cache, const int* block_tables,
+                                        const int* table_offset, const int* token_seq, const int* token_pos,
+                                        void* out, int block_size, float scale, void* workspace,
+                                        size_t workspace_bytes, pkv_stream stream);
+
 /* f3: shared-prefix-aware plan.  llm-engine's prefix cache makes sequences with a
  * common prompt share their leading blocks (KVCacheManager::allocate_prompt,
  * src/kv_cache/block_allocator.cpp:28-78), yet its decode kernels fetch those

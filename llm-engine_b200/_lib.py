@@ -45,6 +45,8 @@ SIGNATURES = {
     "pkv_decode_plan_device": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
     **{f"pkv_decode_attn_planned_peer_{s}": (_i, [C.POINTER(DecodePlan)] + [_vp] * 7 + [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp])
        for s in ("f16", "bf16")},
+    **{f"pkv_append_decode_attn_planned_{s}": (_i, [C.POINTER(DecodePlan)] + [_vp] * 11 + [_i, _f, _vp, _sz, _vp])
+       for s in ("f16", "bf16")},
     "pkv_peer_alloc": (_i, [_sz, _vp, _vp]),
     "pkv_peer_open": (_i, [_vp, _vp]),
     "pkv_peer_close": (_i, [_vp]),

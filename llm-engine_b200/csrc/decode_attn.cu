@@ -182,10 +182,13 @@ int persistent_sms() {
   return sms;
 }
 
-template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MINB, int TOK = 1>
+template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MINB, int TOK = 1, bool FUSED = false>
 int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
+  if constexpr (TOK == 1 && !FUSED) {
+    if (a.new_k != nullptr) return launch_tma<T, D, NT, MT, NSTAGES, WARPS, MINB, 1, true>(a, grid, stream);
+  }
   using S = TmaSmem<D, MT, NSTAGES, WARPS>;
-  auto kern = decode_tma_kernel<T, D, NT, MT, NSTAGES, WARPS, MINB, TOK>;
+  auto kern = decode_tma_kernel<T, D, NT, MT, NSTAGES, WARPS, MINB, TOK, FUSED>;
   static thread_local int configured_device = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -238,12 +241,20 @@ int launch_combine(const DecodeArgs& a, cudaStream_t stream) {
   return check_launch("decode_combine_kernel");
 }
 
+// Whether this geometry runs on decode_tma_kernel.
+template <typename T>
+bool tma_path(const DecodeArgs& a) {
+  if constexpr (IsF32<T>::value) return false;
+  return (a.head_dim == 64 || a.head_dim == 128) && a.group <= 16 && a.bs_log2 >= 4 && a.scale > 0.f && tuning().use_tma &&
+         tensor_map_encoder() != nullptr;
+}
+
 template <typename T>
 int launch_decode_main(const DecodeArgs& a, int grid, cudaStream_t stream, bool* log2_domain) {
   *log2_domain = true;
   if constexpr (!IsF32<T>::value) {
     const bool mma_ok = (a.head_dim == 64 || a.head_dim == 128) && a.group <= 16 && a.bs_log2 >= 0;
-    const bool tma_ok = mma_ok && a.bs_log2 >= 4 && a.scale > 0.f && tuning().use_tma && tensor_map_encoder() != nullptr;
+    const bool tma_ok = tma_path<T>(a);
     if (tma_ok) {
       const int variant = tuning().variant;
       if (a.head_dim == 64) {
@@ -351,6 +362,7 @@ void fill_args(DecodeArgs& a, const void* q, const void* kc, const void* vc, con
   a.out_col0 = 0;
   for (int p = 0; p < kMaxPeers; ++p) { a.peer_out[p] = nullptr; a.peer_flags[p] = nullptr; }
   a.n_peers = 0; a.my_rank = 0; a.epoch = 0;
+  a.new_k = nullptr; a.new_v = nullptr; a.slots = nullptr;
 }
 
 void attach_workspace(DecodeArgs& a, void* workspace, const WsLayout& w) {
@@ -407,6 +419,12 @@ int plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, i
   return PKV_OK;
 }
 
+struct FusedAppend {
+  const void* k;
+  const void* v;
+  const int* slots;
+};
+
 struct PeerSetup {
   void* const* out;      // host array: every rank's full output buffer (device pointers valid on this GPU)
   int* const* flags;     // host array: every rank's flag array
@@ -416,8 +434,9 @@ struct PeerSetup {
 template <typename T>
 int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, const void* vc, const int* bt,
                    const int* to, const int* ts, const int* tp, void* out, int block_size, float scale,
-                   void* workspace, size_t workspace_bytes, pkv_stream stream, const PeerSetup* peers = nullptr) {
-  const char* fn = peers ? "pkv_decode_attn_planned_peer" : "pkv_decode_attn_planned";
+                   void* workspace, size_t workspace_bytes, pkv_stream stream, const PeerSetup* peers = nullptr,
+                   const FusedAppend* app = nullptr) {
+  const char* fn = peers ? "pkv_decode_attn_planned_peer" : (app ? "pkv_append_decode_attn_planned" : "pkv_decode_attn_planned");
   if (!plan) return fail(PKV_E_ARG, "%s: null plan", fn);
   if (plan->n_tokens <= 0) return PKV_OK;
   int st = validate_geometry(fn, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size);
@@ -447,6 +466,14 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
     a.n_peers = peers->n_peers; a.my_rank = peers->my_rank; a.epoch = peers->epoch;
     a.out_row_elems = static_cast<long long>(peers->q_heads_total) * plan->head_dim;
     a.out_col0 = peers->my_rank * plan->q_heads * plan->head_dim;
+  }
+  if (app) {
+    if (!app->k || !app->v || !app->slots) return fail(PKV_E_ARG, "%s: null k, v or slots", fn);
+    if (!tma_path<T>(a))
+      return fail(PKV_E_UNSUPPORTED, "%s: the fused append runs on the TMA kernel only (16-bit K/V, head_dim 64 or 128, at most 16 "
+                  "query heads per kv head, power-of-two block_size >= 16); call pkv_append_* first instead", fn);
+    if (!aligned16(app->k) || !aligned16(app->v)) return fail(PKV_E_ARG, "%s: k and v must be 16-byte aligned", fn);
+    a.new_k = app->k; a.new_v = app->v; a.slots = app->slots;
   }
   const int n_shared = plan->reserved >> 1;
   if (n_shared > 0) {
@@ -851,5 +878,20 @@ PKV_DECODE_ENTRY(f32, float)
 
 PKV_DECODE_PEER_ENTRY(f16, __half)
 PKV_DECODE_PEER_ENTRY(bf16, __nv_bfloat16)
+
+#define PKV_APPEND_DECODE_ENTRY(SUFFIX, TYPE)                                                                        \
+  int pkv_append_decode_attn_planned_##SUFFIX(const pkv_decode_plan* plan, const void* q, const void* k,            \
+                                              const void* v, const int* slots, void* k_cache, void* v_cache,        \
+                                              const int* block_tables, const int* table_offset,                     \
+                                              const int* token_seq, const int* token_pos, void* out,                \
+                                              int block_size, float scale, void* workspace,                         \
+                                              size_t workspace_bytes, pkv_stream stream) {                          \
+    const FusedAppend app{k, v, slots};                                                                              \
+    return decode_planned<TYPE>(plan, q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,   \
+                                block_size, scale, workspace, workspace_bytes, stream, nullptr, &app);              \
+  }
+
+PKV_APPEND_DECODE_ENTRY(f16, __half)
+PKV_APPEND_DECODE_ENTRY(bf16, __nv_bfloat16)
 
 }  // extern "C"

@@ -66,6 +66,12 @@ struct DecodeArgs {
   void* peer_out[kMaxPeers];
   int* peer_flags[kMaxPeers];
   int n_peers, my_rank, epoch;
+  // Append fused into the attention (decode_tma_kernel only; null = off): the unit that reaches a
+  // token's newest key takes that key's K/V row from new_k / new_v [n_tokens][kv_heads*head_dim]
+  // instead of the pool and writes it to pool row slots[token].  k_cache / v_cache are written.
+  const void* new_k;
+  const void* new_v;
+  const int* slots;
 };
 
 // Output row of (token, head 0) under the layout above.

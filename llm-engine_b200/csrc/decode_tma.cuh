@@ -56,7 +56,10 @@ template <int D, int MT, int NSTAGES, int WARPS> struct TmaSmem {
 // the tokens' heads sit side by side in the N dimension (NT / TOK head tiles per token); every
 // token gets its own split-K partial.  Such units come from the shared-prefix planner as
 // SharedItem records (decode_plan.hpp).
-template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS, int TOK = 1>
+// FUSED_APPEND: the unit that reaches a token's newest key takes that row from the step's k / v
+// inputs and writes it to the pool (DecodeArgs::new_k); a separate instantiation, so that the
+// plain kernel carries none of it.
+template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS, int TOK = 1, bool FUSED_APPEND = false>
 __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     decode_tma_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap kmap,
                       const __grid_constant__ CUtensorMap vmap) {
@@ -237,6 +240,29 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
       const uint32_t kst = ring + slot * S::kStageBytes;
       const uint32_t vst = kst + S::kKBytes;
       const int rows_valid = min(SLAB, kv_len - j * SLAB);
+      if constexpr (TOK == 1 && FUSED_APPEND) {
+        if (j == n_slabs - 1 && kv_begin + kv_len == __ldg(a.token_pos + token) + 1) {
+          // Fused append: this unit ends at the token's newest key, whose row is not in the pool yet.
+          // Lanes 0 .. 8 HALVES - 1 bring the 16-byte pieces of its K row, the next 8 HALVES those of
+          // its V row: each goes into the slab just fetched (same swizzle as the TMA boxes) and to
+          // the token's slot in the pool.
+          const int rl = kv_len - 1 - j * SLAB, box = rl >> 4, r = rl & 15;
+          const bool is_v = lane >= 8 * HALVES;
+          const int cidx = lane - (is_v ? 8 * HALVES : 0);
+          if (lane < 16 * HALVES) {
+            const size_t row_off = (static_cast<size_t>(kvh) * D) * sizeof(T) + static_cast<size_t>(cidx) * 16;
+            const size_t kv_row_bytes = static_cast<size_t>(a.kv_heads) * D * sizeof(T);
+            const char* src = static_cast<const char*>(is_v ? a.new_v : a.new_k) + static_cast<size_t>(token) * kv_row_bytes + row_off;
+            const uint4 val = __ldg(reinterpret_cast<const uint4*>(src));
+            char* pool = static_cast<char*>(const_cast<void*>(is_v ? a.v_cache : a.k_cache));
+            *reinterpret_cast<uint4*>(pool + static_cast<size_t>(__ldg(a.slots + token)) * kv_row_bytes + row_off) = val;
+            unsigned char* dst = ring_ptr + slot * S::kStageBytes + (is_v ? S::kKBytes : 0) +
+                                 (box * HALVES + (cidx >> 3)) * kBoxBytes + r * 128 + (((cidx & 7) ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = val;
+          }
+          __syncwarp();
+        }
+      }
       if (rows_valid < SLAB) {
         // Slots past the end of the history hold whatever was there before (or were
         // never fetched): their scores are masked below, and their V rows are

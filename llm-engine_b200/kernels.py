@@ -151,6 +151,16 @@ class DecodePlan:
                                      C.c_float(scale), p, n, _stream(stream))
         _lib.check(fn, st)
 
+    def append_attention(self, q, k, v, slots, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,
+                         block_size: int, scale: float, stream=None) -> None:
+        """launch_store_kv + attention in one chain (decode steps only: one token per sequence)."""
+        fn = f"pkv_append_decode_attn_planned_{_suffix(k_cache)}"
+        p, n = self._ws()
+        st = getattr(_lib.lib(), fn)(C.byref(self.plan), _ptr(q), _ptr(k), _ptr(v), _ptr(slots), _ptr(k_cache), _ptr(v_cache),
+                                     _ptr(block_tables), _ptr(table_offset), _ptr(token_seq), _ptr(token_pos), _ptr(out),
+                                     block_size, C.c_float(scale), p, n, _stream(stream))
+        _lib.check(fn, st)
+
 
 def launch_attention_prefill(q, k_cache, v_cache, block_tables, table_offset, q_start, q_len, ctx_len, out,
                              n_tokens: int, n_seqs: int, max_q_len: int, q_heads: int, kv_heads: int, head_dim: int,

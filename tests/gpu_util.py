@@ -107,9 +107,16 @@ class Case:
         return d
 
     def run_gpu(self, pkv, torch, mode="split", d=None):
-        """mode: direct | split | host_plan | shared_plan | device_plan.  Returns (k_cache bits, v_cache bits, out fp32, dev dict)."""
+        """mode: direct | split | host_plan | shared_plan | device_plan | fused_append.  Returns (k_cache bits, v_cache bits, out fp32, dev dict)."""
         d = d or self.upload(torch)
         kv_dim = self.kvh * self.hd
+        if mode == "fused_append":
+            plan = pkv.DecodePlan(self.N, self.qh, self.kvh, self.hd).build_host(self.idx.token_pos)
+            plan.append_attention(d["q"], d["k"], d["v"], d["slots"], d["kc"], d["vc"], d["block_tables"], d["table_offset"],
+                                  d["token_seq"], d["token_pos"], d["out"], self.bs, self.scale)
+            d["plan"] = plan
+            torch.cuda.synchronize()
+            return d
         pkv.launch_store_kv(d["k"], d["v"], d["slots"], d["kc"], d["vc"], self.N, kv_dim)
         args = (d["q"], d["kc"], d["vc"], d["block_tables"], d["table_offset"], d["token_seq"], d["token_pos"], d["out"])
         if mode == "direct":
