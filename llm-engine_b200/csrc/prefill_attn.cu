@@ -3,14 +3,22 @@
 //
 // llm-engine has no prefill kernel (src/kernels/attention_prefill.cu:1 is a stub):
 // every prompt token goes through the decode kernel and re-reads its whole history.
-// Here a thread block takes 128 consecutive tokens of one sequence's chunk for one
-// query head and walks the keys in tiles of 64, so S = Q K^T and O = P V are dense
+// Here a work item is 128 consecutive tokens of one sequence's chunk for one query
+// head; its keys are walked in tiles of 64, so S = Q K^T and O = P V are dense
 // 128 x 64 x 64 contractions issued as tcgen05.mma with the accumulators in tensor
 // memory.  The result it must agree with is ref::paged_attention_head
 // (include/engine/ops.h:87-111) applied to every (token, head) of the chunk.
 //
+// Thread blocks are persistent, two per SM: each takes items from a ticket counter
+// until none are left, and its roles run ahead of one another across items (the next
+// item's Q and first K/V tiles are fetched, and its first scores computed, while the
+// softmax warps still write the current item's output), which hides the 4,000-cycle
+// start of an item (look-ups through the block table, first loads, first MMA) and the
+// hand-over between blocks that a one-item-per-block grid pays every time.
+//
 // Roles inside a block of 192 threads:
-//   warp 4 (one lane)   TMA producer: the Q tile once, then per key tile four boxes of
+//   warp 4 (one lane)   TMA producer: takes the ticket, publishes the item, loads its Q
+//                       tile into one of two buffers, then per key tile four boxes of
 //                       16 slots x 128 bytes for K and four for V, gathered through the
 //                       block table into a four-stage ring (128-byte swizzle, which is
 //                       also the canonical shared-memory layout of the MMA operands).
@@ -32,6 +40,8 @@
 //
 // Every mbarrier wait is bounded: a wait that runs out sets bit 2 of the device error
 // word and the block carries on to its tear-down (tensor memory is always released).
+#include <algorithm>
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -42,6 +52,12 @@
 namespace pkv {
 
 __device__ unsigned int g_pkv_prefill_error = 0;
+
+// Ticket and completion counters of the persistent kernel, one pair per launch in flight (the host
+// hands out slots round-robin); the last block of a launch leaves its pair at zero.
+constexpr int kTicketSlots = 64;
+__device__ unsigned int g_prefill_ticket[kTicketSlots];
+__device__ unsigned int g_prefill_done[kTicketSlots];
 
 namespace {
 
@@ -54,9 +70,9 @@ constexpr int kBox = 16 * 128;                   // one TMA box: 16 slots x 128 
 constexpr int kQBytes = kQTile * 128;            // 128 rows x 128 bytes
 constexpr int kKBytes = kKTile * 128;            // one K (or V, or P) tile: 64 keys x 128 bytes / 128 rows x 64 keys
 constexpr int kSmemQ = 0;
-constexpr int kSmemKV = kSmemQ + kQBytes;                    // kKVStages x (K, V)
+constexpr int kSmemKV = kSmemQ + 2 * kQBytes;                // two Q tiles (this item's and the next), then kKVStages x (K, V)
 constexpr int kSmemOnes = kSmemKV + kKVStages * 2 * kKBytes; // a V-shaped tile of 1.0: P x ones = row sums
-constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 89 KB: two blocks per SM
+constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 105 KB: two blocks per SM
 constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
 constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64) with the row sums right behind (16)
 constexpr float kRescaleThreshold = 8.f;                     // in log2 units: P stays below 2^8
@@ -71,6 +87,10 @@ struct PrefillArgs {
   int q_heads, kv_heads, group;
   int block_size, bs_log2;
   float scale;
+  // persistent scheduling: items = sequences x query-tile slots x heads, handed out by a ticket counter
+  unsigned int* ticket;
+  unsigned int* done;
+  int n_items, n_qtiles_max;
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
@@ -160,6 +180,14 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 __device__ __forceinline__ void give_up() { atomicOr(&g_pkv_prefill_error, 4u); }
 
+// What the TMA producer publishes about the work item it has fetched; the other roles read it
+// from shared memory once the item's Q tile barrier has completed.
+struct ItemDesc {
+  int n_kt;        // key tiles; -1: no more items
+  int head, row0, rows_here, kv_total, limit0;   // limit0 = last visible key position of row 0
+  int pad[2];
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
     prefill_tc_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap qmap,
@@ -170,7 +198,8 @@ __global__ void __launch_bounds__(kThreads, 2)
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[1 + 2 * kKVStages + 6];
+  __shared__ __align__(8) unsigned long long bars[4 + 2 * kKVStages + 6];
+  __shared__ __align__(16) ItemDesc s_item[2];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,11 +208,14 @@ __global__ void __launch_bounds__(kThreads, 2)
   const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sOnes = base + kSmemOnes;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = KV_FULL + kKVStages, S_FULL = KV_EMPTY + kKVStages, P_FULL = S_FULL + 2, PV_DONE = P_FULL + 2 };
+  enum { Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = KV_FULL + kKVStages, S_FULL = KV_EMPTY + kKVStages, P_FULL = S_FULL + 2, PV_DONE = P_FULL + 2 };
 
   // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
   if (threadIdx.x == 0) {
-    mbar_init(BAR(Q_FULL), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(BAR(Q_FULL + i), 1);
+      mbar_init(BAR(Q_EMPTY + i), 1 + 128);   // tcgen05.commit after the item's last Q K^T, and every softmax thread once it has read the item
+    }
     for (int i = 0; i < kKVStages; ++i) {
       mbar_init(BAR(KV_FULL + i), 1);
       mbar_init(BAR(KV_EMPTY + i), 1);   // arrived by tcgen05.commit after P_j V_j
@@ -194,6 +226,14 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated
     }
     mbar_fence_init();
+  }
+  if (threadIdx.x < kKTile) {
+    // the tile of ones that makes columns 64..79 of every P V product the row sums of P
+    const uint32_t one2 = pack2<T>(1.f, 1.f);
+    unsigned char* orow = base_ptr + kSmemOnes + threadIdx.x * 128;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(orow + ch * 16) = make_uint4(one2, one2, one2, one2);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
@@ -207,20 +247,14 @@ __global__ void __launch_bounds__(kThreads, 2)
   pdl_launch_dependents();
   pdl_wait();
 
-  const int seq = blockIdx.z;
-  const int head = blockIdx.x;
-  const int q_len = __ldg(a.q_len + seq);
-  const int n_qtiles = (q_len + kQTile - 1) / kQTile;
-  const int tile = n_qtiles - 1 - static_cast<int>(blockIdx.y);  // longest key ranges first
-  const bool active = tile >= 0;                                 // uniform for the whole block
-  const int ctx = __ldg(a.ctx_len + seq);
-  const int row0 = __ldg(a.q_start + seq) + tile * kQTile;       // first packed row of this tile
-  const int rows_here = min(kQTile, q_len - tile * kQTile);
-  const int kv_total = ctx + tile * kQTile + rows_here;          // keys 0 .. kv_total-1 are visible to the tile
-  const int n_kt = active ? (kv_total + kKTile - 1) / kKTile : 0;
-  const int kvh = head / a.group;
-  // After a wait has run out (here or in an earlier block of this launch) no further
-  // wait spins: the block falls through its schedule and releases its tensor memory.
+  // The block is persistent: it takes (sequence, query tile, head) items from a ticket counter until
+  // none are left.  Every role runs its own loop over the items and keeps its own running counts of
+  // items (n) and key tiles (g), from which ring stages, buffers and barrier parities follow; the
+  // roles are coupled only through the barriers, so the producer prefetches the next item's Q and
+  // first K/V tiles, and the MMA thread computes its first scores, while the softmax warps are
+  // still writing the current item's output.
+  // After a wait has run out (here or in an earlier block of this launch) no further wait spins:
+  // the block falls through its schedule and releases its tensor memory.
   bool dead = *reinterpret_cast<volatile unsigned int*>(&g_pkv_prefill_error) != 0u;
   auto WAIT = [&](uint32_t bar, uint32_t parity) {
     if (dead) return;
@@ -230,42 +264,83 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   };
 
-  if (!active) {
-    // nothing to do for this tile index; fall through to the tear-down
-  } else if (warp == 4) {
+  if (warp == 4) {
     // ================================ TMA producer ================================
-    const int* tbl = a.block_tables + __ldg(a.table_offset + seq);
-    if (lane == 0) {
-      mbar_arrive_expect_tx(BAR(Q_FULL), kQBytes);
-      tma_load_2d(sQ, &qmap, head * kHd, row0, BAR(Q_FULL));
-    }
-    for (int j = 0; j < n_kt; ++j) {
-      const int st = j % kKVStages;
-      const int rel = j * kKTile + (lane & 3) * 16;
-      int ent = 0;
-      if (rel < kv_total) ent = __ldg(tbl + (rel >> a.bs_log2));
-      int y[4];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const int e = __shfl_sync(0xffffffffu, ent, b);
-        y[b] = (e << a.bs_log2) + ((j * kKTile + 16 * b) & (a.block_size - 1));
+    int n = 0, g = 0;
+    for (;;) {
+      dead = __shfl_sync(0xffffffffu, dead ? 1 : 0, 0) != 0;   // only lane 0 waits: keep the warp in step
+      // next item that has work: items are numbered heads fastest (the heads of a group share their
+      // K/V tiles through L2), then the sequence's query tiles from the longest key range down, then
+      // sequences
+      ItemDesc d;
+      int seq = 0;
+      d.n_kt = -1;
+      while (!dead) {
+        unsigned t = 0;
+        if (lane == 0) t = atomicAdd(a.ticket, 1u);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= static_cast<unsigned>(a.n_items)) break;
+        const int head = static_cast<int>(t % a.q_heads);
+        const int rest = static_cast<int>(t / a.q_heads);
+        const int slot_y = rest % a.n_qtiles_max;
+        seq = rest / a.n_qtiles_max;
+        const int q_len = __ldg(a.q_len + seq);
+        const int tile = (q_len + kQTile - 1) / kQTile - 1 - slot_y;
+        if (tile < 0) continue;
+        const int ctx = __ldg(a.ctx_len + seq);
+        d.head = head;
+        d.row0 = __ldg(a.q_start + seq) + tile * kQTile;
+        d.rows_here = min(kQTile, q_len - tile * kQTile);
+        d.kv_total = ctx + tile * kQTile + d.rows_here;
+        d.limit0 = ctx + tile * kQTile;
+        d.n_kt = (d.kv_total + kKTile - 1) / kKTile;
+        break;
       }
+      const int qb = n & 1;
       if (lane == 0) {
-        WAIT(BAR(KV_EMPTY + st), ((j / kKVStages) & 1) ^ 1);
-        int nvalid = 0;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) nvalid += (j * kKTile + 16 * b < kv_total) ? 1 : 0;
-        mbar_arrive_expect_tx(BAR(KV_FULL + st), static_cast<uint32_t>(nvalid) * 2u * kBox);
-        const uint32_t kdst = sKV + st * 2 * kKBytes, vdst = kdst + kKBytes;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          if (j * kKTile + 16 * b < kv_total) {
-            tma_load_2d(kdst + b * kBox, &kmap, kvh * kHd, y[b], BAR(KV_FULL + st));
-            tma_load_2d(vdst + b * kBox, &vmap, kvh * kHd, y[b], BAR(KV_FULL + st));
-          }
+        WAIT(BAR(Q_EMPTY + qb), ((n >> 1) & 1) ^ 1);
+        s_item[qb] = d;
+        if (d.n_kt > 0 && !dead) {
+          mbar_arrive_expect_tx(BAR(Q_FULL + qb), kQBytes);
+          tma_load_2d(sQ + qb * kQBytes, &qmap, d.head * kHd, d.row0, BAR(Q_FULL + qb));
+        } else {
+          s_item[qb].n_kt = -1;
+          mbar_arrive(BAR(Q_FULL + qb));        // "no more items"
         }
       }
-      __syncwarp();
+      dead = __shfl_sync(0xffffffffu, dead ? 1 : 0, 0) != 0;
+      if (d.n_kt <= 0 || dead) break;
+      const int kvh = d.head / a.group;
+      const int* tbl = a.block_tables + __ldg(a.table_offset + seq);
+      for (int j = 0; j < d.n_kt; ++j, ++g) {
+        const int st = g % kKVStages;
+        const int rel = j * kKTile + (lane & 3) * 16;
+        int ent = 0;
+        if (rel < d.kv_total) ent = __ldg(tbl + (rel >> a.bs_log2));
+        int y[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int e = __shfl_sync(0xffffffffu, ent, b);
+          y[b] = (e << a.bs_log2) + ((j * kKTile + 16 * b) & (a.block_size - 1));
+        }
+        if (lane == 0) {
+          WAIT(BAR(KV_EMPTY + st), ((g / kKVStages) & 1) ^ 1);
+          int nvalid = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) nvalid += (j * kKTile + 16 * b < d.kv_total) ? 1 : 0;
+          mbar_arrive_expect_tx(BAR(KV_FULL + st), static_cast<uint32_t>(nvalid) * 2u * kBox);
+          const uint32_t kdst = sKV + st * 2 * kKBytes, vdst = kdst + kKBytes;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            if (j * kKTile + 16 * b < d.kv_total) {
+              tma_load_2d(kdst + b * kBox, &kmap, kvh * kHd, y[b], BAR(KV_FULL + st));
+              tma_load_2d(vdst + b * kBox, &vmap, kvh * kHd, y[b], BAR(KV_FULL + st));
+            }
+          }
+        }
+        __syncwarp();
+      }
+      ++n;
     }
   } else if (warp == 5) {
     // ================================ MMA issuer ================================
@@ -274,40 +349,51 @@ __global__ void __launch_bounds__(kThreads, 2)
     // memory), a blocking try_wait costs a few hundred cycles even on a completed phase (mbar_wait
     // looks first), and the scalar code of a lone thread runs at one dependent instruction every
     // few cycles, so the schedule is kept to two waits, eight MMAs and three commits per key tile:
-    //  * no separate "S buffer free" barrier: a softmax thread has read S_{j-1} and written P_{j-1}
-    //    over it before it arrives on P_FULL_{j-1}; this thread waits for that, issues P_{j-1} V_{j-1},
-    //    and only then S_{j+1} into the same buffer (instructions of one thread execute in order);
+    //  * no separate "S buffer free" barrier: a softmax thread has read S_{g-1} and written P_{g-1}
+    //    over it before it arrives on P_FULL_{g-1}; this thread waits for that, issues P_{g-1} V_{g-1},
+    //    and only then S_{g+1} into the same buffer (instructions of one thread execute in order);
     //  * O += P V and the row sums of P come out of ONE MMA of N = 80: the B operand is MN-major,
     //    its first 64 columns are the V tile and its next column block, one leading-dimension
     //    offset away, is a tile of ones.
+    // It does not wait for the softmax warps' epilogue: after an item's last P V it goes on to the
+    // next item's first scores.
     if (lane == 0) {
       const uint64_t desc_q0 = smem_desc(sQ), desc_k0 = smem_desc(sKV);
-      WAIT(BAR(Q_FULL), 0);
-      auto issue_qk = [&](int j) {
-        const int st = j % kKVStages, sb = j & 1;
-        WAIT(BAR(KV_FULL + st), (j / kKVStages) & 1);
-        tc_fence_after();
-        // descriptors differ only in their 14-bit start-address field: add to the low word
-        const uint64_t kd = desc_k0 + ((st * 2 * kKBytes) >> 4);
+      int n = 0, g = 0;
+      while (!dead) {
+        const int qb = n & 1;
+        WAIT(BAR(Q_FULL + qb), (n >> 1) & 1);
+        const int n_kt = s_item[qb].n_kt;
+        if (n_kt <= 0 || dead) break;
+        const uint64_t desc_q = desc_q0 + ((qb * kQBytes) >> 4);
+        auto issue_qk = [&](int gg, bool last_of_item) {
+          const int st = gg % kKVStages, sb = gg & 1;
+          WAIT(BAR(KV_FULL + st), (gg / kKVStages) & 1);
+          tc_fence_after();
+          // descriptors differ only in their 14-bit start-address field: add to the low word
+          const uint64_t kd = desc_k0 + ((st * 2 * kKBytes) >> 4);
 #pragma unroll
-        for (int ks = 0; ks < kHd / 16; ++ks)
-          tc_mma(tmem + kTmemS + sb * 64, desc_q0 + 2 * ks, kd + 2 * ks, kIdescQK, ks > 0);
-        tc_commit(BAR(S_FULL + sb));
-      };
-      issue_qk(0);
-      for (int j = 0; j < n_kt; ++j) {
-        const int st = j % kKVStages, sb = j & 1;
-        if (j + 1 < n_kt) issue_qk(j + 1);
-        WAIT(BAR(P_FULL + sb), (j >> 1) & 1);
-        tc_fence_after();
-        const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
-        const uint64_t vd = smem_desc(v_base, sOnes - v_base);
-        const uint32_t p_addr = tmem + kTmemS + sb * 64;      // P(j) lies over the first 32 columns of S(j)
+          for (int ks = 0; ks < kHd / 16; ++ks)
+            tc_mma(tmem + kTmemS + sb * 64, desc_q + 2 * ks, kd + 2 * ks, kIdescQK, ks > 0);
+          tc_commit(BAR(S_FULL + sb));
+          if (last_of_item) tc_commit(BAR(Q_EMPTY + qb));      // the Q tile has been read for the last time
+        };
+        issue_qk(g, n_kt == 1);
+        for (int j = 0; j < n_kt; ++j, ++g) {
+          const int st = g % kKVStages, sb = g & 1;
+          if (j + 1 < n_kt) issue_qk(g + 1, j + 2 == n_kt);
+          WAIT(BAR(P_FULL + sb), (g >> 1) & 1);
+          tc_fence_after();
+          const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
+          const uint64_t vd = smem_desc(v_base, sOnes - v_base);
+          const uint32_t p_addr = tmem + kTmemS + sb * 64;      // P lies over the first 32 columns of its S buffer
 #pragma unroll
-        for (int kk = 0; kk < kKTile / 16; ++kk)
-          tc_mma_ts(tmem + kTmemO, p_addr + kk * 8, vd + kk * (kBox >> 4), kIdescPV, (j | kk) != 0);
-        tc_commit(BAR(KV_EMPTY + st));
-        tc_commit(BAR(PV_DONE + sb));
+          for (int kk = 0; kk < kKTile / 16; ++kk)
+            tc_mma_ts(tmem + kTmemO, p_addr + kk * 8, vd + kk * (kBox >> 4), kIdescPV, (j | kk) != 0);
+          tc_commit(BAR(KV_EMPTY + st));
+          tc_commit(BAR(PV_DONE + sb));
+        }
+        ++n;
       }
     }
     __syncwarp();
@@ -315,133 +401,133 @@ __global__ void __launch_bounds__(kThreads, 2)
     // ================================ softmax warps ================================
     const int r = threadIdx.x;                      // row of the tile == tensor-memory lane
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    const int limit = ctx + tile * kQTile + min(r, rows_here - 1);   // last visible key position of this row
     const float sl2 = a.scale * kLog2e;
-    // the tile of ones that turns the second MMA of every k-step into a row sum
-    if (r < kKTile) {
-      const uint32_t one2 = pack2<T>(1.f, 1.f);
-      unsigned char* orow = base_ptr + kSmemOnes + r * 128;
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(orow + ch * 16) = make_uint4(one2, one2, one2, one2);
-    }
-    // Reference maximum of the row.  It follows the true running maximum lazily: O and the row
-    // sum stay in tensor memory and are only rescaled when the maximum has grown by more than
-    // 2^8, so most tiles cost no read-modify-write of the accumulator at all.
-    float m_used = -INFINITY;
+    int n = 0, g = 0;
+    while (!dead) {
+      const int qb = n & 1;
+      WAIT(BAR(Q_FULL + qb), (n >> 1) & 1);
+      const ItemDesc d = s_item[qb];
+      mbar_arrive(BAR(Q_EMPTY + qb));                 // the item's description has been read
+      if (d.n_kt <= 0 || dead) break;
+      const int n_kt = d.n_kt, kv_total = d.kv_total, rows_here = d.rows_here;
+      const int limit = d.limit0 + min(r, rows_here - 1);   // last visible key position of this row
+      // Reference maximum of the row.  It follows the true running maximum lazily: O and the row
+      // sum stay in tensor memory and are only rescaled when the maximum has grown by more than
+      // 2^8, so most tiles cost no read-modify-write of the accumulator at all.
+      float m_used = -INFINITY;
 
-    for (int j = 0; j < n_kt; ++j) {
-      const int sb = j & 1;
-      const int k0 = j * kKTile;
-      WAIT(BAR(S_FULL + sb), (j >> 1) & 1);
-      tc_fence_after();
-      float sc[kKTile];
-      {
-        uint32_t v0[32], v1[32];
-        tc_ld32(tmem + lane_addr + kTmemS + sb * 64, v0);
-        tc_ld32(tmem + lane_addr + kTmemS + sb * 64 + 32, v1);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          sc[i] = __uint_as_float(v0[i]);
-          sc[32 + i] = __uint_as_float(v1[i]);
-        }
-      }
-      tc_fence_before();                             // the scores are in registers; arriving on P_FULL below
-                                                     // also tells the MMA thread that S may be overwritten
-      // Causal mask, only on tiles that reach past some row's last visible key (warp-uniform test).
-      if (__any_sync(0xffffffffu, k0 + kKTile - 1 > limit)) {
-#pragma unroll
-        for (int i = 0; i < kKTile; ++i)
-          if (k0 + i > limit) sc[i] = -INFINITY;
-      }
-      // Row maximum: eight independent chains of three-input maxima, two scores a step.
-      float mx8[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(sc[u], sc[8 + u]);
-#pragma unroll
-      for (int i = 16; i < kKTile; i += 16)
-#pragma unroll
-        for (int u = 0; u < 8; ++u) mx8[u] = max3(mx8[u], sc[i + u], sc[i + 8 + u]);
-      const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), fmaxf(max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-      if (j == 0) {
-        m_used = mx;                                 // finite: key 0 is visible to every row
-      } else if (__any_sync(0xffffffffu, (mx - m_used) * sl2 > kRescaleThreshold)) {
-        // Rare: bring this warp's rows of O and of the row sums to the new maximum.  Each thread
-        // owns its own tensor-memory lane; P_{j-1} V_{j-1} must have landed and P_j V_j cannot start
-        // before this thread has arrived on P_FULL below.
-        WAIT(BAR(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1);
+      for (int j = 0; j < n_kt; ++j, ++g) {
+        const int sb = g & 1;
+        const int k0 = j * kKTile;
+        WAIT(BAR(S_FULL + sb), (g >> 1) & 1);
         tc_fence_after();
-        const float m_new = fmaxf(m_used, mx);
-        const float f = ex2_approx((m_used - m_new) * sl2);
-        m_used = m_new;
-#pragma unroll
-        for (int blk = 0; blk < 3; ++blk) {          // O: columns 128..191, row sums: 192..223
-          uint32_t v[32];
-          tc_ld32(tmem + lane_addr + kTmemO + blk * 32, v);
+        float sc[kKTile];
+        {
+          uint32_t v0[32], v1[32];
+          tc_ld32(tmem + lane_addr + kTmemS + sb * 64, v0);
+          tc_ld32(tmem + lane_addr + kTmemS + sb * 64 + 32, v1);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-          tc_st32(tmem + lane_addr + kTmemO + blk * 32, v);
+          for (int i = 0; i < 32; ++i) {
+            sc[i] = __uint_as_float(v0[i]);
+            sc[32 + i] = __uint_as_float(v1[i]);
+          }
+        }
+        // Causal mask, only on tiles that reach past some row's last visible key (warp-uniform test).
+        if (__any_sync(0xffffffffu, k0 + kKTile - 1 > limit)) {
+#pragma unroll
+          for (int i = 0; i < kKTile; ++i)
+            if (k0 + i > limit) sc[i] = -INFINITY;
+        }
+        // Row maximum: eight independent chains of three-input maxima, two scores a step.
+        float mx8[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(sc[u], sc[8 + u]);
+#pragma unroll
+        for (int i = 16; i < kKTile; i += 16)
+#pragma unroll
+          for (int u = 0; u < 8; ++u) mx8[u] = max3(mx8[u], sc[i + u], sc[i + 8 + u]);
+        const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), fmaxf(max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        if (j == 0) {
+          m_used = mx;                                 // finite: key 0 is visible to every row
+        } else if (__any_sync(0xffffffffu, (mx - m_used) * sl2 > kRescaleThreshold)) {
+          // Rare: bring this warp's rows of O and of the row sums to the new maximum.  Each thread
+          // owns its own tensor-memory lane; the previous tile's P V must have landed and this tile's
+          // cannot start before this thread has arrived on P_FULL below.
+          WAIT(BAR(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1);
+          tc_fence_after();
+          const float m_new = fmaxf(m_used, mx);
+          const float f = ex2_approx((m_used - m_new) * sl2);
+          m_used = m_new;
+#pragma unroll
+          for (int blk = 0; blk < 3; ++blk) {          // O: columns 128..191, row sums: 192..223
+            uint32_t v[32];
+            tc_ld32(tmem + lane_addr + kTmemO + blk * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tc_st32(tmem + lane_addr + kTmemO + blk * 32, v);
+          }
+        }
+        const float neg = -m_used * sl2;
+        // P goes back into tensor memory as packed 16-bit pairs over the first 32 columns of the S
+        // buffer it came from: this thread has all of its own row in registers, and the MMA thread
+        // overwrites the buffer with the scores after next only after it has issued this P V.
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[i] = pack2<T>(ex2_approx(fmaf(sc[c * 32 + 2 * i], sl2, neg)), ex2_approx(fmaf(sc[c * 32 + 2 * i + 1], sl2, neg)));
+          tc_st16(tmem + lane_addr + kTmemS + sb * 64 + c * 16, pk);
+        }
+        if (j == n_kt - 1 && kv_total - k0 < kKTile) {
+          // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
+          // behind them are whatever the pool or the ring held; clear them so 0 * x stays 0.
+          const int st = g % kKVStages;
+          WAIT(BAR(KV_FULL + st), (g / kKVStages) & 1);
+          if (r < kKTile && r >= kv_total - k0) {
+            unsigned char* vrow = base_ptr + kSmemKV + st * 2 * kKBytes + kKBytes + r * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vrow + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the cleared rows before the MMA reads them
         }
         tc_wait_st();
         tc_fence_before();
+        mbar_arrive(BAR(P_FULL + sb));
       }
-      const float neg = -m_used * sl2;
-      // P goes back into tensor memory as packed 16-bit pairs over the first 32 columns of the S
-      // buffer it came from: this thread has all of its own row in registers, and the MMA thread
-      // overwrites the buffer with S(j+2) only after it has issued P(j) V(j).
+      // epilogue: O / row sum.  The next item's first P V cannot overwrite O before this thread has
+      // arrived on that tile's P_FULL, which it does after the loads below.
+      WAIT(BAR(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1);
+      tc_fence_after();
+      {
+        uint32_t o0[32], o1[32], lv[32];
+        tc_ld32(tmem + lane_addr + kTmemO, o0);
+        tc_ld32(tmem + lane_addr + kTmemO + 32, o1);
+        tc_ld32(tmem + lane_addr + kTmemL, lv);
+        tc_wait_ld();
+        tc_fence_before();
+        if (r < rows_here) {
+          const float inv = 1.f / __uint_as_float(lv[0]);
+          T* orow = static_cast<T*>(a.out) + (static_cast<size_t>(d.row0 + r) * a.q_heads + d.head) * kHd;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          pk[i] = pack2<T>(ex2_approx(fmaf(sc[c * 32 + 2 * i], sl2, neg)), ex2_approx(fmaf(sc[c * 32 + 2 * i + 1], sl2, neg)));
-        tc_st16(tmem + lane_addr + kTmemS + sb * 64 + c * 16, pk);
-      }
-      if (j == n_kt - 1 && kv_total - k0 < kKTile) {
-        // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
-        // behind them are whatever the pool or the ring held; clear them so 0 * x stays 0.
-        const int st = j % kKVStages;
-        WAIT(BAR(KV_FULL + st), (j / kKVStages) & 1);
-        if (r < kKTile && r >= kv_total - k0) {
-          unsigned char* vrow = base_ptr + kSmemKV + st * 2 * kKBytes + kKBytes + r * 128;
-#pragma unroll
-          for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(vrow + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the cleared rows before the MMA reads them
-      }
-      if (j == 0) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tile of ones, likewise
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(BAR(P_FULL + sb));
-    }
-    // epilogue: O / row sum
-    WAIT(BAR(PV_DONE + ((n_kt - 1) & 1)), ((n_kt - 1) >> 1) & 1);
-    tc_fence_after();
-    {
-      uint32_t o0[32], o1[32], lv[32];
-      tc_ld32(tmem + lane_addr + kTmemO, o0);
-      tc_ld32(tmem + lane_addr + kTmemO + 32, o1);
-      tc_ld32(tmem + lane_addr + kTmemL, lv);
-      tc_wait_ld();
-      if (r < rows_here) {
-        const float inv = 1.f / __uint_as_float(lv[0]);
-        T* orow = static_cast<T*>(a.out) + (static_cast<size_t>(row0 + r) * a.q_heads + head) * kHd;
-#pragma unroll
-        for (int d = 0; d < 32; d += 8) {
-          uint4 w0, w1;
-          w0.x = pack2<T>(__uint_as_float(o0[d]) * inv, __uint_as_float(o0[d + 1]) * inv);
-          w0.y = pack2<T>(__uint_as_float(o0[d + 2]) * inv, __uint_as_float(o0[d + 3]) * inv);
-          w0.z = pack2<T>(__uint_as_float(o0[d + 4]) * inv, __uint_as_float(o0[d + 5]) * inv);
-          w0.w = pack2<T>(__uint_as_float(o0[d + 6]) * inv, __uint_as_float(o0[d + 7]) * inv);
-          w1.x = pack2<T>(__uint_as_float(o1[d]) * inv, __uint_as_float(o1[d + 1]) * inv);
-          w1.y = pack2<T>(__uint_as_float(o1[d + 2]) * inv, __uint_as_float(o1[d + 3]) * inv);
-          w1.z = pack2<T>(__uint_as_float(o1[d + 4]) * inv, __uint_as_float(o1[d + 5]) * inv);
-          w1.w = pack2<T>(__uint_as_float(o1[d + 6]) * inv, __uint_as_float(o1[d + 7]) * inv);
-          *reinterpret_cast<uint4*>(orow + d) = w0;
-          *reinterpret_cast<uint4*>(orow + 32 + d) = w1;
+          for (int dd = 0; dd < 32; dd += 8) {
+            uint4 w0, w1;
+            w0.x = pack2<T>(__uint_as_float(o0[dd]) * inv, __uint_as_float(o0[dd + 1]) * inv);
+            w0.y = pack2<T>(__uint_as_float(o0[dd + 2]) * inv, __uint_as_float(o0[dd + 3]) * inv);
+            w0.z = pack2<T>(__uint_as_float(o0[dd + 4]) * inv, __uint_as_float(o0[dd + 5]) * inv);
+            w0.w = pack2<T>(__uint_as_float(o0[dd + 6]) * inv, __uint_as_float(o0[dd + 7]) * inv);
+            w1.x = pack2<T>(__uint_as_float(o1[dd]) * inv, __uint_as_float(o1[dd + 1]) * inv);
+            w1.y = pack2<T>(__uint_as_float(o1[dd + 2]) * inv, __uint_as_float(o1[dd + 3]) * inv);
+            w1.z = pack2<T>(__uint_as_float(o1[dd + 4]) * inv, __uint_as_float(o1[dd + 5]) * inv);
+            w1.w = pack2<T>(__uint_as_float(o1[dd + 6]) * inv, __uint_as_float(o1[dd + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + dd) = w0;
+            *reinterpret_cast<uint4*>(orow + 32 + dd) = w1;
+          }
         }
       }
+      ++n;
     }
   }
   tc_fence_before();
@@ -449,6 +535,15 @@ __global__ void __launch_bounds__(kThreads, 2)
   if (warp == 5) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+  // The last block out resets the ticket counter for the next launch that uses this slot.
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.done, 1u) == gridDim.x - 1) {
+      *a.ticket = 0u;
+      *a.done = 0u;
+      __threadfence();
+    }
   }
 }
 
@@ -511,8 +606,35 @@ int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const 
   a.q_heads = q_heads; a.kv_heads = kv_heads; a.group = q_heads / kv_heads;
   a.block_size = block_size; a.bs_log2 = bsl;
   a.scale = scale;
-  const dim3 grid(q_heads, (max_q_len + kQTile - 1) / kQTile, n_seqs);
-  launch_pdl(kern, grid, dim3(kThreads), kSmemTotal, static_cast<cudaStream_t>(stream), a, qmap, kmap, vmap);
+  a.n_qtiles_max = (max_q_len + kQTile - 1) / kQTile;
+  const long long n_items = static_cast<long long>(n_seqs) * a.n_qtiles_max * q_heads;
+  if (n_items > 0x7fffffffll) return fail(PKV_E_UNSUPPORTED, "%s: %lld work items; at most 2^31 - 1 per call", fn, n_items);
+  a.n_items = static_cast<int>(n_items);
+  // Ticket counters: one pair per launch in flight, taken round-robin; found once per device.
+  static std::atomic<unsigned> launch_seq{0};
+  static thread_local int counters_device = -1;
+  static thread_local unsigned int* ticket_base = nullptr;
+  static thread_local unsigned int* done_base = nullptr;
+  if (counters_device != dev) {
+    void *t = nullptr, *d = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&t, g_prefill_ticket);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&d, g_prefill_done);
+    if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: cudaGetSymbolAddress: %s", fn, cudaGetErrorString(e));
+    ticket_base = static_cast<unsigned int*>(t);
+    done_base = static_cast<unsigned int*>(d);
+    counters_device = dev;
+  }
+  const unsigned slot = launch_seq.fetch_add(1) % kTicketSlots;
+  a.ticket = ticket_base + slot;
+  a.done = done_base + slot;
+  // Persistent blocks: two per SM, or one per item if there are fewer.
+  static thread_local int sms = 0;
+  if (!sms) {
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int blocks = static_cast<int>(std::min<long long>(n_items, 2ll * sms));
+  launch_pdl(kern, dim3(blocks), dim3(kThreads), kSmemTotal, static_cast<cudaStream_t>(stream), a, qmap, kmap, vmap);
   return check_launch("prefill_tc_kernel");
 }
 
