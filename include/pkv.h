@@ -299,7 +299,10 @@ int pkv_peer_free(void* ptr);
  * (both bound the TMA descriptors); max_q_len >= max_s q_len[s] sizes the grid (the
  * caller's chunk size, include/engine/scheduler.h:26).  bf16 and f16, head_dim 64,
  * block_size a power of two >= 16, q_heads % kv_heads == 0; other geometries return
- * PKV_E_UNSUPPORTED (such steps go through pkv_decode_attn_*, as in the reference). */
+ * PKV_E_UNSUPPORTED (such steps go through pkv_decode_attn_*, as in the reference).
+ * The kernel is persistent and hands its work out through a ticket counter taken
+ * from a pool of 64 inside the library: at most 64 prefill launches may be in
+ * flight on one GPU at a time (streams included). */
 int pkv_prefill_attn_bf16(const void* q, const void* k_cache, const void* v_cache,
                           const int* block_tables, const int* table_offset, const int* q_start,
                           const int* q_len, const int* ctx_len, void* out, int n_tokens, int n_seqs,
