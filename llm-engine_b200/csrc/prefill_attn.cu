@@ -407,7 +407,6 @@ __global__ void __launch_bounds__(kThreads, 2)
       const int qb = n & 1;
       WAIT(BAR(Q_FULL + qb), (n >> 1) & 1);
       const ItemDesc d = s_item[qb];
-      mbar_arrive(BAR(Q_EMPTY + qb));                 // the item's description has been read
       if (d.n_kt <= 0 || dead) break;
       const int n_kt = d.n_kt, kv_total = d.kv_total, rows_here = d.rows_here;
       const int limit = d.limit0 + min(r, rows_here - 1);   // last visible key position of this row
@@ -508,25 +507,42 @@ __global__ void __launch_bounds__(kThreads, 2)
         tc_ld32(tmem + lane_addr + kTmemL, lv);
         tc_wait_ld();
         tc_fence_before();
-        if (r < rows_here) {
-          const float inv = 1.f / __uint_as_float(lv[0]);
-          T* orow = static_cast<T*>(a.out) + (static_cast<size_t>(d.row0 + r) * a.q_heads + d.head) * kHd;
+        // The row goes through shared memory so that the global stores are whole 128-byte lines
+        // (eight lanes per row) instead of 32 scattered 16-byte pieces per instruction.  The staging
+        // area is the item's own Q tile, which nothing reads any more (the item's last Q K^T has
+        // completed); each warp stages and drains its own 32 rows, 16-byte pieces XOR-swizzled
+        // against bank conflicts.
+        const float inv = 1.f / __uint_as_float(lv[0]);
+        unsigned char* stage = base_ptr + kSmemQ + qb * kQBytes;
+        unsigned char* my_row = stage + r * 128;
 #pragma unroll
-          for (int dd = 0; dd < 32; dd += 8) {
-            uint4 w0, w1;
-            w0.x = pack2<T>(__uint_as_float(o0[dd]) * inv, __uint_as_float(o0[dd + 1]) * inv);
-            w0.y = pack2<T>(__uint_as_float(o0[dd + 2]) * inv, __uint_as_float(o0[dd + 3]) * inv);
-            w0.z = pack2<T>(__uint_as_float(o0[dd + 4]) * inv, __uint_as_float(o0[dd + 5]) * inv);
-            w0.w = pack2<T>(__uint_as_float(o0[dd + 6]) * inv, __uint_as_float(o0[dd + 7]) * inv);
-            w1.x = pack2<T>(__uint_as_float(o1[dd]) * inv, __uint_as_float(o1[dd + 1]) * inv);
-            w1.y = pack2<T>(__uint_as_float(o1[dd + 2]) * inv, __uint_as_float(o1[dd + 3]) * inv);
-            w1.z = pack2<T>(__uint_as_float(o1[dd + 4]) * inv, __uint_as_float(o1[dd + 5]) * inv);
-            w1.w = pack2<T>(__uint_as_float(o1[dd + 6]) * inv, __uint_as_float(o1[dd + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + dd) = w0;
-            *reinterpret_cast<uint4*>(orow + 32 + dd) = w1;
-          }
+        for (int dd = 0; dd < 32; dd += 8) {
+          uint4 w0, w1;
+          w0.x = pack2<T>(__uint_as_float(o0[dd]) * inv, __uint_as_float(o0[dd + 1]) * inv);
+          w0.y = pack2<T>(__uint_as_float(o0[dd + 2]) * inv, __uint_as_float(o0[dd + 3]) * inv);
+          w0.z = pack2<T>(__uint_as_float(o0[dd + 4]) * inv, __uint_as_float(o0[dd + 5]) * inv);
+          w0.w = pack2<T>(__uint_as_float(o0[dd + 6]) * inv, __uint_as_float(o0[dd + 7]) * inv);
+          w1.x = pack2<T>(__uint_as_float(o1[dd]) * inv, __uint_as_float(o1[dd + 1]) * inv);
+          w1.y = pack2<T>(__uint_as_float(o1[dd + 2]) * inv, __uint_as_float(o1[dd + 3]) * inv);
+          w1.z = pack2<T>(__uint_as_float(o1[dd + 4]) * inv, __uint_as_float(o1[dd + 5]) * inv);
+          w1.w = pack2<T>(__uint_as_float(o1[dd + 6]) * inv, __uint_as_float(o1[dd + 7]) * inv);
+          *reinterpret_cast<uint4*>(my_row + ((((dd >> 3)) ^ (r & 7)) << 4)) = w0;
+          *reinterpret_cast<uint4*>(my_row + ((((dd >> 3) + 4) ^ (r & 7)) << 4)) = w1;
+        }
+        __syncwarp();
+        T* obase = static_cast<T*>(a.out) + (static_cast<size_t>(d.row0) * a.q_heads + d.head) * kHd;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = warp * 32 + i * 4 + (lane >> 3), ch = lane & 7;
+          const uint4 w = *reinterpret_cast<const uint4*>(stage + row * 128 + ((ch ^ (row & 7)) << 4));
+          if (row < rows_here)
+            *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(obase + static_cast<size_t>(row) * a.q_heads * kHd) + ch * 16) = w;
         }
       }
+      // The Q buffer may be refilled (by TMA) once every thread is done with it: the item's
+      // description, and the staging of its output.
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      mbar_arrive(BAR(Q_EMPTY + qb));
       ++n;
     }
   }
