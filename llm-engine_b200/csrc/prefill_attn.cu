@@ -171,6 +171,14 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Two fused multiply-adds in one instruction (packed fp32 pairs): (a0, a1) * (s, s) + (n, n).
+__device__ __forceinline__ void ffma2(float a0, float a1, float s, float n, float& r0, float& r1) {
+  asm("{\n .reg .b64 ra, rs, rn, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rs, {%4, %4};\n mov.b64 rn, {%5, %5};\n"
+      " fma.rn.f32x2 rd, ra, rs, rn;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(r0), "=f"(r1)
+      : "f"(a0), "f"(a1), "f"(s), "f"(n));
+}
+
 // Three-input maximum: one instruction on this architecture.
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -476,8 +484,11 @@ __global__ void __launch_bounds__(kThreads, 2)
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            pk[i] = pack2<T>(ex2_approx(fmaf(sc[c * 32 + 2 * i], sl2, neg)), ex2_approx(fmaf(sc[c * 32 + 2 * i + 1], sl2, neg)));
+          for (int i = 0; i < 16; ++i) {
+            float x0, x1;
+            ffma2(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1], sl2, neg, x0, x1);
+            pk[i] = pack2<T>(ex2_approx(x0), ex2_approx(x1));
+          }
           tc_st16(tmem + lane_addr + kTmemS + sb * 64 + c * 16, pk);
         }
         if (j == n_kt - 1 && kv_total - k0 < kKTile) {
