@@ -136,3 +136,63 @@ def test_cfg4_chunked_prefill_sampled_at_full_size(pkv, orc, torch_cuda, workloa
     a = d["out"][mid].float().cpu().numpy().reshape(-1, 64)
     b = out_before[mid].float().cpu().numpy().reshape(-1, 64)
     assert rel_errors(a, b)[1] <= 2e-2
+
+
+def test_more_items_than_resident_blocks_and_empty_tile_slots(pkv, orc, torch_cuda):
+    """The kernel's blocks are persistent and take (sequence, tile, head) items from a ticket counter:
+    here 300 short sequences x 8 heads x 3 tile slots (max_q_len 300, most chunks far shorter, so most
+    slots are empty) give 7,200 tickets for 296 blocks."""
+    rng = np.random.default_rng(31)
+    S = 300
+    ctx = [int(x) for x in rng.integers(0, 200, size=S)]
+    new = [int(x) for x in rng.integers(1, 140, size=S)]
+    new[17], new[255] = 300, 257
+    case = make_case(orc, pkv, "bf16", 8, 2, 16, ctx, new, seed=23)
+    _, _, want = case.expected(orc, threads=8)
+    d = run_prefill(pkv, torch_cuda, case)
+    _, got = from_device(torch_cuda, orc, d["out"], "bf16")
+    assert np.isfinite(got).all()
+    e_ref, e_row = rel_errors(got.reshape(-1, 64), want.reshape(-1, 64))
+    assert e_ref <= TOL["bf16"] and e_row <= TOL["bf16"], (e_ref, e_row)
+
+
+def test_launches_in_a_row_and_on_two_streams_keep_their_ticket_counters_apart(pkv, orc, torch_cuda):
+    """70 launches in a row (the pool of ticket counters has 64 slots and every launch must leave its
+    slot at zero), then two different steps launched on two streams at once."""
+    torch = torch_cuda
+    a = make_case(orc, pkv, "bf16", 14, 2, 16, [0, 300, 77], [200, 129, 64], seed=24)
+    b = make_case(orc, pkv, "bf16", 8, 8, 16, [50, 0], [150, 260], seed=25)
+    wants = [c.expected(orc, threads=8)[2] for c in (a, b)]
+    da = run_prefill(pkv, torch, a)
+    first = da["out"].clone()
+    for _ in range(70):
+        da["out"].zero_()
+        run_prefill(pkv, torch, a, d=da)
+        assert torch.equal(first, da["out"])
+    db = b.upload(torch)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for case, d, st in ((a, da, streams[0]), (b, db, streams[1])):
+        d["out"].zero_()
+        with torch.cuda.stream(st):
+            for _ in range(5):
+                run_prefill_async(pkv, torch, case, d)
+    torch.cuda.synchronize()
+    assert pkv.debug_device_flags() == 0
+    for case, d, want in ((a, da, wants[0]), (b, db, wants[1])):
+        _, got = from_device(torch, orc, d["out"], "bf16")
+        e_ref, e_row = rel_errors(got.reshape(-1, 64), want.reshape(-1, 64))
+        assert e_ref <= TOL["bf16"] and e_row <= TOL["bf16"], (e_ref, e_row)
+
+
+def run_prefill_async(pkv, torch, case, d):
+    """run_prefill without the synchronisation, on the current stream."""
+    i32 = lambda x: torch.from_numpy(np.ascontiguousarray(x, dtype=np.int32)).cuda()
+    if "pf_idx" not in d:
+        q_len = np.asarray(case.seq_new, dtype=np.int32)
+        d["pf_idx"] = (i32(np.concatenate([[0], np.cumsum(q_len)[:-1]])), i32(q_len), i32(np.asarray(case.seq_ctx)), int(q_len.max()), len(q_len))
+        torch.cuda.synchronize()
+    qs, ql, cl, mx, ns = d["pf_idx"]
+    pkv.launch_store_kv(d["k"], d["v"], d["slots"], d["kc"], d["vc"], case.N, case.kvh * case.hd)
+    pkv.launch_attention_prefill(d["q"], d["kc"], d["vc"], d["block_tables"], d["table_offset"], qs, ql, cl, d["out"], case.N, ns, mx,
+                                 case.qh, case.kvh, case.hd, case.bs, case.nb, case.scale)
