@@ -75,6 +75,7 @@ constexpr int kSmemOnes = kSmemKV + kKVStages * 2 * kKBytes; // a V-shaped tile 
 constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 105 KB: two blocks per SM
 constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
 constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64) with the row sums right behind (16)
+constexpr int kMaxRanked = 256;       // launches of up to this many (sequence, tile) groups hand them out longest first
 constexpr float kRescaleThreshold = 8.f;                     // in log2 units: P stays below 2^8
 
 struct PrefillArgs {
@@ -90,7 +91,7 @@ struct PrefillArgs {
   // persistent scheduling: items = sequences x query-tile slots x heads, handed out by a ticket counter
   unsigned int* ticket;
   unsigned int* done;
-  int n_items, n_qtiles_max;
+  int n_items, n_qtiles_max, n_seqs;
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
@@ -255,6 +256,35 @@ __global__ void __launch_bounds__(kThreads, 2)
   pdl_launch_dependents();
   pdl_wait();
 
+  // Order in which the (sequence, query tile) groups are handed out: longest key range first, so that
+  // the launch ends on its shortest items and the blocks finish together (with the natural order the
+  // last blocks ran up to a tenth of the launch alone).  Every block ranks the groups itself, once:
+  // a few hundred comparisons per thread for up to kMaxRanked groups; larger launches keep the
+  // natural order, whose tail matters less the more items there are.
+  __shared__ int s_key[kMaxRanked];
+  __shared__ short s_order[kMaxRanked];
+  const int n_groups = a.n_seqs * a.n_qtiles_max;
+  const bool ranked = n_groups <= kMaxRanked;
+  if (ranked) {
+    for (int j = threadIdx.x; j < n_groups; j += kThreads) {
+      const int z = j / a.n_qtiles_max, y = j - z * a.n_qtiles_max;
+      const int ql = __ldg(a.q_len + z);
+      const int nt = (ql + kQTile - 1) / kQTile;
+      s_key[j] = y < nt ? __ldg(a.ctx_len + z) + min((nt - y) * kQTile, ql) : -1;   // keys that tile sees; -1: no such tile
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < n_groups; j += kThreads) {
+      const int kj = s_key[j];
+      int rank = 0;
+      for (int k = 0; k < n_groups; ++k) {
+        const int kk = s_key[k];
+        rank += (kk > kj || (kk == kj && k < j)) ? 1 : 0;
+      }
+      s_order[rank] = static_cast<short>(j);
+    }
+    __syncthreads();
+  }
+
   // The block is persistent: it takes (sequence, query tile, head) items from a ticket counter until
   // none are left.  Every role runs its own loop over the items and keeps its own running counts of
   // items (n) and key tiles (g), from which ring stages, buffers and barrier parities follow; the
@@ -277,9 +307,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     int n = 0, g = 0;
     for (;;) {
       dead = __shfl_sync(0xffffffffu, dead ? 1 : 0, 0) != 0;   // only lane 0 waits: keep the warp in step
-      // next item that has work: items are numbered heads fastest (the heads of a group share their
-      // K/V tiles through L2), then the sequence's query tiles from the longest key range down, then
-      // sequences
+      // next item that has work: heads fastest (the heads of a group share their K/V tiles through
+      // L2), groups in the order ranked above (or: a sequence's query tiles from the longest key
+      // range down, then sequences)
       ItemDesc d;
       int seq = 0;
       d.n_kt = -1;
@@ -289,7 +319,8 @@ __global__ void __launch_bounds__(kThreads, 2)
         t = __shfl_sync(0xffffffffu, t, 0);
         if (t >= static_cast<unsigned>(a.n_items)) break;
         const int head = static_cast<int>(t % a.q_heads);
-        const int rest = static_cast<int>(t / a.q_heads);
+        int rest = static_cast<int>(t / a.q_heads);
+        if (ranked) rest = s_order[rest];
         const int slot_y = rest % a.n_qtiles_max;
         seq = rest / a.n_qtiles_max;
         const int q_len = __ldg(a.q_len + seq);
@@ -634,6 +665,7 @@ int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const 
   a.block_size = block_size; a.bs_log2 = bsl;
   a.scale = scale;
   a.n_qtiles_max = (max_q_len + kQTile - 1) / kQTile;
+  a.n_seqs = n_seqs;
   const long long n_items = static_cast<long long>(n_seqs) * a.n_qtiles_max * q_heads;
   if (n_items > 0x7fffffffll) return fail(PKV_E_UNSUPPORTED, "%s: %lld work items; at most 2^31 - 1 per call", fn, n_items);
   a.n_items = static_cast<int>(n_items);
