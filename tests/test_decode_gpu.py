@@ -21,7 +21,7 @@ MODES = ["direct", "split", "host_plan", "device_plan"]
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
 def test_cfg1_qwen_layer(pkv, orc, torch_cuda, workloads, dtype, mode):
-    """BASELINE configuration 1: 14 query / 2 kv heads, head_dim 64, 8 sequences with contexts
+    """Configuration 1: 14 query / 2 kv heads, head_dim 64, 8 sequences with contexts
     U[64,512], block 16 in a 4,096-block shuffled pool, one appended token per sequence."""
     w = workloads.make("cfg1")
     case = Case(orc, dtype, w.q_heads, w.kv_heads, w.head_dim, w.block_size, w.num_blocks,
