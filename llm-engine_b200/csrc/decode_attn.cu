@@ -459,6 +459,8 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
                   peers->q_heads_total, peers->n_peers, plan->q_heads);
     for (int p = 0; p < peers->n_peers; ++p) {
       if (!peers->out[p] || !peers->flags[p]) return fail(PKV_E_ARG, "%s: null peer pointer for rank %d", fn, p);
+      if ((reinterpret_cast<uintptr_t>(peers->out[p]) & 15) || (reinterpret_cast<uintptr_t>(peers->flags[p]) & 3))
+        return fail(PKV_E_ARG, "%s: rank %d's output buffer must be 16-byte aligned and its flags 4-byte aligned", fn, p);
       a.peer_out[p] = peers->out[p];
       a.peer_flags[p] = peers->flags[p];
     }

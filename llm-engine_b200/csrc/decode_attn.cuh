@@ -252,10 +252,19 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
         const int head = head0 + r;
         const float4 r4 = merge_partials4<LOG2>(a, ts, head, d4, D);
         T* o = out_row<T>(a, a.out, token) + static_cast<size_t>(head) * D + 4 * d4;
-        o[0] = Elem<T>::from_f32(r4.x);
-        o[1] = Elem<T>::from_f32(r4.y);
-        o[2] = Elem<T>::from_f32(r4.z);
-        o[3] = Elem<T>::from_f32(r4.w);
+        if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {   // one 8-byte store instead of four 2-byte ones
+          uint2 packed = make_uint2(0u, 0u);
+          if constexpr (sizeof(T) == 2) {
+            packed.x = pack2<T>(r4.x, r4.y);
+            packed.y = pack2<T>(r4.z, r4.w);
+          }
+          *reinterpret_cast<uint2*>(o) = packed;
+        } else {
+          o[0] = Elem<T>::from_f32(r4.x);
+          o[1] = Elem<T>::from_f32(r4.y);
+          o[2] = Elem<T>::from_f32(r4.z);
+          o[3] = Elem<T>::from_f32(r4.w);
+        }
       }
     } else {
       for (int idx = threadIdx.x; idx < a.group * D; idx += kCombineThreads) {
