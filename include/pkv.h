@@ -4,11 +4,16 @@
  * This is the whole drop-in boundary: plain pointers and sizes, no C++ or
  * framework types.  Every entry point returns a status code (0 = PKV_OK,
  * negative = error, see pkv_status_string / pkv_last_error), never throws,
- * never synchronises the device, never allocates device memory, and enqueues
+ * never synchronises the device (pkv_debug_device_flags excepted) and enqueues
  * its work on the CUDA stream it is given (NULL = the legacy default stream,
  * which is what llm-engine passes at every call site,
- * src/model/cuda/cuda_model.cu:347-390).  All data pointers are DEVICE pointers
- * unless a parameter is named h_* or documented as host memory.
+ * src/model/cuda/cuda_model.cu:347-390).  Device memory is allocated in two
+ * places only, both set-up code outside the per-step calls: pkv_peer_alloc /
+ * pkv_peer_open (buffers of the head-sharded exchange) and the grow-only scratch
+ * behind the three engine::launch_* symbols the library also exports for an
+ * unmodified llm-engine (their signatures carry no workspace argument).  All data
+ * pointers are DEVICE pointers unless a parameter is named h_* or documented as
+ * host memory.
  *
  * Each declaration names the llm-engine interface it replaces (file:line within
  * that project).  Layout conventions are llm-engine's own:
@@ -61,7 +66,7 @@ const char* pkv_last_error(void);
  * No llm-engine counterpart. */
 int pkv_debug_device_flags(unsigned int* flags);
 
-/* ------------------------------------------------------------------ a1 ----
+/* ----------------------------------------------------------- K/V append ----
  * K/V append.  Replaces engine::launch_store_kv (include/engine/cuda_kernels.h:43-45,
  * src/kernels/store_kv.cu:20-36) and the CPU memcpy pair
  * (src/model/cpu/cpu_model.cpp:153-157):
@@ -77,7 +82,7 @@ int pkv_append_bf16(const void* k, const void* v, const int* slots, void* k_cach
 int pkv_append_f32(const void* k, const void* v, const int* slots, void* k_cache, void* v_cache,
                    int n_tokens, int kv_dim, pkv_stream stream);
 
-/* ------------------------------------------------------------------ f1 ----
+/* -------------------------------------------------------- RoPE + append ----
  * RoPE fused into the append.  Replaces the three launches llm-engine makes per layer,
  * launch_rope(q), launch_rope(k), launch_store_kv (src/model/cuda/cuda_model.cu:366-368,
  * src/kernels/rope.cu:32-62; arithmetic of ref::rope_inplace, include/engine/ops.h:56-68):
@@ -100,7 +105,7 @@ int pkv_rope_append_f32(void* q, const void* k, const void* v, const int* positi
                         const float* sin_table, const int* slots, void* k_cache, void* v_cache, int n_tokens,
                         int q_heads, int kv_heads, int head_dim, pkv_stream stream);
 
-/* ------------------------------------------------------------------ a2 ----
+/* ----------------------------------------------------- decode attention ----
  * Paged decode attention.  Replaces engine::launch_attention_decode and
  * engine::launch_attention_decode_gqa (include/engine/cuda_kernels.h:48-62,
  * src/kernels/attention_decode.cu:133-161, src/kernels/attention_decode_gqa.cu:200-232);
@@ -141,7 +146,9 @@ int pkv_decode_attn_f32(const void* q, const void* k_cache, const void* v_cache,
  *     heads, 4,400 at 14); use pkv_decode_attn_bf16 with your own workspace then;
  *   - the first call on each device looks the area's address up
  *     (cudaGetSymbolAddress, with that device current): make that first call before
- *     any stream capture begins;
+ *     any stream capture begins.  The address is then kept per device ordinal for the
+ *     life of the process, which is the life of the device's primary context: a
+ *     process that calls cudaDeviceReset must not use this entry point afterwards;
  *   - every call on a device shares the one area and rebuilds all of it that it reads
  *     (the plan is rewritten at each call), so nothing needs clearing between calls,
  *     but two calls that overlap on the GPU (different streams) race: serialise them.
@@ -203,7 +210,7 @@ int pkv_append_decode_attn_planned_bf16(const pkv_decode_plan* plan, const void*
                                         void* out, int block_size, float scale, void* workspace,
                                         size_t workspace_bytes, pkv_stream stream);
 
-/* f3: shared-prefix-aware plan.  llm-engine's prefix cache makes sequences with a
+/* Shared-prefix-aware plan.  llm-engine's prefix cache makes sequences with a
  * common prompt share their leading blocks (KVCacheManager::allocate_prompt,
  * src/kv_cache/block_allocator.cpp:28-78), yet its decode kernels fetch those
  * blocks once per sequence.  Given the host copies of the step's index arrays (the
@@ -238,7 +245,7 @@ int pkv_decode_attn_planned_f32(const pkv_decode_plan* plan, const void* q, cons
                                 const int* token_seq, const int* token_pos, void* out, int block_size,
                                 float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
 
-/* ------------------------------------------------------------------ e -----
+/* -------------------------------------------------- head-sharded decode ----
  * Head-sharded decode over the GPUs of one box (one process per GPU).  The path
  * scales by sequence without any exchange, and that is what the benchmark reports;
  * this variant is for a configuration whose kv heads divide the GPU count and
@@ -283,7 +290,7 @@ int pkv_peer_open(const void* handle64, void** ptr);
 int pkv_peer_close(void* ptr);
 int pkv_peer_free(void* ptr);
 
-/* ------------------------------------------------------------------ a3 ----
+/* ---------------------------------------------------- prefill attention ----
  * Paged (chunked) prefill attention on the tensor cores.  llm-engine has no such
  * kernel (src/kernels/attention_prefill.cu:1 is a stub; prefill tokens go through
  * the decode launcher, src/model/cuda/cuda_model.cu:370-377); the result it must
@@ -314,7 +321,7 @@ int pkv_prefill_attn_f16(const void* q, const void* k_cache, const void* v_cache
                          int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
                          int num_blocks, float scale, pkv_stream stream);
 
-/* ------------------------------------------------------------------ a5 ----
+/* ----------------------------------------------------------- block copy ----
  * Prefix-cache copy-on-write block copy.  No llm-engine counterpart (it shares
  * full blocks only and therefore never copies, docs/design.md:36); semantics are
  * memcpy's: for each pair i, block src_dst_pairs[2i] is copied over block
@@ -331,7 +338,7 @@ int pkv_copy_blocks_f32(void* k_cache, void* v_cache, const int* src_dst_pairs, 
 int pkv_copy_blocks_layers(void* const* d_cache_ptrs, int n_caches, const int* src_dst_pairs,
                            int n_pairs, size_t block_bytes, pkv_stream stream);
 
-/* ------------------------------------------------------------------ a4 ----
+/* -------------------------------------------------- step indices (host) ----
  * Step-index packing (host).  Replaces the loop of CudaModel::upload_step_indices
  * (src/model/cuda/cuda_model.cu:453-473): sequences are numbered in order of
  * first appearance among the packed tokens, each distinct sequence's block table
@@ -347,7 +354,7 @@ int pkv_step_pack(int n_tokens, const uint64_t* tok_seq_key, const int32_t* cons
                   int* token_seq, int* tables, size_t tables_cap, int* table_offset,
                   size_t offsets_cap, int* n_seqs, int* n_table);
 
-/* ------------------------------------------------------------------ f2 ----
+/* ------------------------------------------------ step indices (device) ----
  * Step-index build on the device.  Replaces all of CudaModel::upload_step_indices
  * (src/model/cuda/cuda_model.cu:453-491): its O(N*S) host loop and its six
  * synchronous host-to-device copies per step, which is what stands between the
@@ -374,7 +381,7 @@ int pkv_step_pack_device(const int32_t* d_updates, int n_updates, const int32_t*
                          int tokens_cap, int32_t* d_tables, int tables_cap, int32_t* d_table_offset,
                          int32_t* d_counts, pkv_stream stream);
 
-/* ------------------------------------------------------------------ a0 ----
+/* ---------------------------------------------------- block bookkeeping ----
  * KV block bookkeeping (host).  C handles over the C++ KVCacheManager / BlockTable
  * of include/pkv_kv_cache.hpp, which keep the public surface of llm-engine's
  * classes (include/engine/kv_cache.h:21-99, src/kv_cache/block_allocator.cpp:8-142)

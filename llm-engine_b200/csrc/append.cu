@@ -1,4 +1,4 @@
-// K/V append (include/pkv.h, section a1): scatter each new token's K and V row to
+// K/V append (include/pkv.h, "K/V append"): scatter each new token's K and V row to
 // row slots[t] of the block pool.  A pure byte copy, so one kernel serves every
 // element type; the dtype-suffixed entry points only fix the row size.
 //

@@ -1,4 +1,4 @@
-// Prefix-cache copy-on-write block copy (include/pkv.h, section a5).
+// Prefix-cache copy-on-write block copy (include/pkv.h, "block copy").
 //
 // A block of one pool is block_size * kv_dim elements of contiguous memory, so the
 // copy of pair (src, dst) in pool p is a straight 16-byte-vector memcpy of

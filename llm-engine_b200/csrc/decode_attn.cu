@@ -1,4 +1,4 @@
-// C-ABI entry points for paged decode attention (include/pkv.h, section a2):
+// C-ABI entry points for paged decode attention (include/pkv.h, "decode attention"):
 // argument validation, split-K planning (host and device), kernel selection.
 #include <algorithm>
 #include <cstdlib>

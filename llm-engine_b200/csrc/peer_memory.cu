@@ -1,4 +1,4 @@
-// Set-up helpers for the head-sharded exchange (include/pkv.h, section e): device buffers that
+// Set-up helpers for the head-sharded exchange (include/pkv.h, "head-sharded decode"): device buffers that
 // the other GPUs of the box can store into.  One process per GPU: a rank allocates its buffer,
 // hands the 64-byte handle to the other ranks by whatever channel the caller has (the bench and
 // the tests use torch.distributed), and every rank opens every other rank's handle.  These four

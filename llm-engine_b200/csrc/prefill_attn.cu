@@ -1,5 +1,5 @@
 // Paged (chunked) prefill attention on the 5th-generation tensor cores (sm_100a):
-// entry points of include/pkv.h, section a3.
+// entry points of include/pkv.h, "prefill attention".
 //
 // llm-engine has no prefill kernel (src/kernels/attention_prefill.cu:1 is a stub):
 // every prompt token goes through the decode kernel and re-reads its whole history.

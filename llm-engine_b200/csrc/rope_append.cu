@@ -1,4 +1,4 @@
-// RoPE fused into the K/V append (include/pkv.h, section f1).
+// RoPE fused into the K/V append (include/pkv.h, "RoPE + append").
 //
 // llm-engine runs three launches per layer here: rope(q), rope(k), store_kv
 // (src/model/cuda/cuda_model.cu:366-368; the fusion is the first item of its own

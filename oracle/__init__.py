@@ -26,9 +26,15 @@ ORC_PATH = os.path.join(_HERE, "liborc.so")
 REF_PATH = os.path.join(_HERE, "_ref", "libpkv_ref.so")
 
 
+def reference_root() -> str:
+    """Where the llm-engine source tree is looked for: $LLM_ENGINE_REFERENCE, else the
+    Makefile's default.  It need not exist (a prebuilt ``_ref/libpkv_ref.so`` is used then)."""
+    return os.environ.get("LLM_ENGINE_REFERENCE", "/root/reference")
+
+
 def build(verbose: bool = False) -> None:
     """Compile ``liborc.so`` and, where the reference tree is present, ``_ref/libpkv_ref.so``."""
-    out = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    out = subprocess.run(["make", "-C", _HERE, "REF=" + reference_root()], capture_output=True, text=True)
     if verbose or out.returncode != 0:
         print(out.stdout + out.stderr)
     if out.returncode != 0:

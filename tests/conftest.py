@@ -50,7 +50,7 @@ def orc():
 def ref():
     """The reference's own sources compiled behind oracle/ref_shim.cpp, or None."""
     import oracle
-    if not os.path.exists(oracle.REF_PATH) and os.path.isdir("/root/reference/include/engine"):
+    if not os.path.exists(oracle.REF_PATH) and os.path.isdir(os.path.join(oracle.reference_root(), "include", "engine")):
         oracle.build()
     return oracle.load_ref()
 

@@ -37,21 +37,31 @@ def main():
         idx = [i32(case.idx.block_tables), i32(case.idx.table_offset), i32(case.idx.token_seq), i32(case.idx.token_pos)]
         pkv.launch_store_kv(d["k"], d["v"], i32(case.idx.slots), d["kc"], d["vc"], case.N, kvl * hd)
         plan = pkv.DecodePlan(case.N, ql, kvl, hd, device=dev).build_host(case.idx.token_pos)
-        ex = sharding.HeadShardedExchange(case.N, qh, hd, d["q"].dtype, dist, dev)
-        for rep in range(3):                              # the flags are reused from call to call
-            out = ex.attention(plan, d["q"], d["kc"], d["vc"], *idx, bs, case.scale)
-            torch.cuda.synchronize()
-            _, got = from_device(torch, orc, out, dtype)
-            e_ref, e_row = rel_errors(got.reshape(case.N * qh, hd), want.reshape(case.N * qh, hd))
-            assert e_ref <= TOL[dtype] and e_row <= TOL[dtype], (rank, dtype, rep, e_ref, e_row)
-            dist.barrier()                                # nobody overwrites a buffer a peer is still checking
         # this rank's own columns are what the ordinary call computes for the same heads, bit for bit
         local = torch.zeros((case.N, ql * hd), dtype=d["q"].dtype, device=dev)
         plan.attention(d["q"], d["kc"], d["vc"], *idx, local, bs, case.scale)
         torch.cuda.synchronize()
-        assert torch.equal(local.view(torch.int16), out[:, q0 * hd:(q0 + ql) * hd].contiguous().view(torch.int16))
-        assert pkv.debug_device_flags() == 0
-        ex.close()
+        # Both ways of numbering the calls: counted on the device (epoch argument 0, the form a CUDA
+        # graph replays) and passed by the host as a growing epoch.  A fresh set of buffers each, since
+        # the flags of one form would satisfy the other's first waits.
+        for device_epoch in (True, False):
+            ex = sharding.HeadShardedExchange(case.N, qh, hd, d["q"].dtype, dist, dev)
+            for rep in range(3):                          # the flags are reused from call to call
+                ex.out.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()                            # every rank's buffer is cleared before anybody stores into it
+                out = ex.attention(plan, d["q"], d["kc"], d["vc"], *idx, bs, case.scale, device_epoch=device_epoch)
+                torch.cuda.synchronize()
+                _, got = from_device(torch, orc, out, dtype)
+                e_ref, e_row = rel_errors(got.reshape(case.N * qh, hd), want.reshape(case.N * qh, hd))
+                assert e_ref <= TOL[dtype] and e_row <= TOL[dtype], (rank, dtype, device_epoch, rep, e_ref, e_row)
+                assert torch.equal(local.view(torch.int16), out[:, q0 * hd:(q0 + ql) * hd].contiguous().view(torch.int16)), \
+                    (rank, dtype, device_epoch, rep, "own columns differ from the ordinary call")
+                dist.barrier()                            # nobody overwrites a buffer a peer is still checking
+            assert pkv.debug_device_flags() == 0
+            ex.close()
+        print(f"rank {rank}: {dtype}: full output within {TOL[dtype]} of the checker, own columns bit-identical to the "
+              f"ordinary call, device-counted and host-passed epochs, 3 calls each", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: head-sharded decode matches the checker on all {world} ranks", flush=True)

@@ -6,8 +6,10 @@ import subprocess
 
 import pytest
 
+import oracle
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = "/root/reference"
+REF = oracle.reference_root()
 LIBDIR = os.path.join(ROOT, "llm-engine_b200")
 
 needs_ref = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "include", "engine")),

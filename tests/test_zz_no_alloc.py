@@ -3,8 +3,8 @@ workspace (an engine that has already given all free HBM to its block pool, or a
 loop that must not hit cudaMalloc's device synchronisation).
 
 Called through the C ABI twice in a row -- the second call on different inputs, reusing the
-same built-in area -- and compared with the ordinary entry point fed a caller-owned workspace,
-within the 2e-2 the bf16 parity tests use.  Collected last on purpose (file name), so a run
+same built-in area -- and compared both with the ordinary entry point fed a caller-owned
+workspace and with the CPU checker, within the 2e-2 the bf16 parity tests use.  Collected last on purpose (file name), so a run
 that stops at the first failure has already run every other test; it also passes alone in a
 fresh process."""
 import ctypes as C
@@ -46,6 +46,10 @@ def test_builtin_scratch_matches_caller_workspace_on_two_calls(pkv, orc, torch_c
         assert np.isfinite(a).all()
         e_ref, e_row = rel_errors(a.reshape(-1, 64), b.reshape(-1, 64))
         assert e_ref <= TOL["bf16"] and e_row <= TOL["bf16"], (seed, e_ref, e_row)
+        # and against the CPU checker itself, not only against the library's other entry point
+        _, _, want_cpu = case.expected(orc)
+        e_ref, e_row = rel_errors(a.reshape(-1, 64), want_cpu.reshape(-1, 64))
+        assert e_ref <= TOL["bf16"] and e_row <= TOL["bf16"], (seed, "checker", e_ref, e_row)
 
 
 def test_builtin_scratch_rejects_steps_beyond_its_size(pkv, torch_cuda):
