@@ -45,6 +45,7 @@ WORKLOAD_TEXT = {
     "cfg3": "TinyLlama-1.1B decode step: 22 layers, 32q/4kv heads, d64, bf16 KV, 256 seqs, ctx log-uniform [128,8192], block 16, fragmented 65536-block pool per layer",
     "cfg4": "chunked prefill, Qwen2.5-0.5B attention shapes (14q/2kv heads, d64), bf16: 32 seqs, cached context U[0,1536] + 512-token chunk, causal over cached+new, block 16, shuffled tables; one step = append + prefill attention for 24 layers",
     "cfg5": "prefix-cache decode: TinyLlama shapes, 22 layers, 128 seqs sharing a 512-token prefix + suffix U[32,256], bf16 KV, block 16",
+    "cow": "copy-on-write block copy alone: TinyLlama shapes (4 kv heads, d64, bf16, block 16: 8 KiB blocks), 22 layers x 2 pools of 8192 blocks, 127 block pairs per wave on every pool in one launch, 8 disjoint pair lists in rotation",
 }
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the decode attention kernel, from the
 # ncu captures summarised under profiles/ (same per-launch workload as the default seed of each configuration).
@@ -123,72 +124,98 @@ def physical_gpu_index(local: int) -> int:
 # ------------------------------------------------------------------------------------
 # CPU arm: the reference's own implementation of the path on the host cores.
 # ------------------------------------------------------------------------------------
-def cpu_step_sample(w, checker, threads, layer_pools=None, seed=0):
-    """Times ONE layer of the step (append + attention for every sequence) on the host and
-    returns (seconds for that layer, description).  Pools are fp32, as in the reference's CPU
-    backend; bf16 workloads are rounded to bf16 and widened first."""
+def load_workloads_standalone():
+    """The workload generator, loaded from its file so that the CPU arm never imports the product
+    package (and therefore never loads libpkv.so)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("pkv_workloads", os.path.join(ROOT, "llm-engine_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["pkv_workloads"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def pack_step_numpy(w):
+    """Index arrays of the step as CudaModel::upload_step_indices builds them
+    (src/model/cuda/cuda_model.cu:453-473), in numpy: sequences in packed order, each table once."""
+    bs = w.block_size
+    seq = np.repeat(np.arange(w.n_seqs, dtype=np.int32), w.new.astype(np.int64))
+    first = np.concatenate([[0], np.cumsum(w.new)[:-1]])
+    pos = (np.repeat(w.ctx, w.new.astype(np.int64)) + (np.arange(seq.size) - np.repeat(first, w.new.astype(np.int64)))).astype(np.int32)
+    tables = np.concatenate([np.asarray(t, dtype=np.int32) for t in w.tables])
+    off = np.concatenate([[0], np.cumsum([len(t) for t in w.tables])[:-1]]).astype(np.int32)
+    slots = (tables[off[seq] + pos // bs].astype(np.int64) * bs + pos % bs).astype(np.int32)
+    return {"slots": slots, "token_seq": seq, "token_pos": pos, "block_tables": tables, "table_offset": off, "n_tokens": int(seq.size)}
+
+
+def cpu_step_fn(w, checker, threads, seed=0):
+    """Returns (step, n_tokens): step() runs the WHOLE step on the host -- for every layer, append the
+    batch's K/V rows and run paged attention for every sequence -- and returns its wall time.  Pools
+    are fp32, as in the reference's CPU backend (bf16 workloads are rounded to bf16 and widened first);
+    one K pool and one V pool are reused by every layer: configuration 3 reads 0.8 GB of their rows per
+    layer, far beyond the last-level cache, so reuse does not flatter the number."""
     import oracle
     orc = oracle.load_orc()
-    pkv = importlib.import_module("llm-engine_b200")
     rng = np.random.default_rng(seed)
     bs, kv_dim = w.block_size, w.kv_dim
-    tabs, pos, _ = w.step_tokens()
-    idx = pkv.pack_step(tabs, pos, bs)
-    N = idx.n_tokens
+    idx = pack_step_numpy(w)
+    N = idx["n_tokens"]
     slots_total = w.num_blocks * bs
-    if layer_pools is not None:
-        kc, vc = layer_pools
-    else:
-        # Only slots that some sequence owns are read; filling the whole pool costs host time for nothing.
-        kc = np.zeros((slots_total, kv_dim), dtype=np.float32)
-        vc = np.zeros((slots_total, kv_dim), dtype=np.float32)
-        used = np.unique(idx.block_tables)
-        rows = (used[:, None].astype(np.int64) * bs + np.arange(bs)[None, :]).reshape(-1)
-        for a in (kc, vc):
-            vals = rng.standard_normal((rows.size, kv_dim), dtype=np.float32)
-            a[rows] = orc.from_bf16_bits(orc.to_bf16_bits(vals)) if w.dtype == "bf16" else vals
+    # Only slots that some sequence owns are read; filling the whole pool costs host time for nothing.
+    kc = np.zeros((slots_total, kv_dim), dtype=np.float32)
+    vc = np.zeros((slots_total, kv_dim), dtype=np.float32)
+    used = np.unique(idx["block_tables"])
+    rows = (used[:, None].astype(np.int64) * bs + np.arange(bs)[None, :]).reshape(-1)
     cast = (lambda a: orc.from_bf16_bits(orc.to_bf16_bits(a))) if w.dtype == "bf16" else (lambda a: a)
+    for a in (kc, vc):
+        a[rows] = cast(rng.standard_normal((rows.size, kv_dim), dtype=np.float32))
     q = cast(rng.standard_normal((N, w.q_heads * w.head_dim), dtype=np.float32))
     k = cast(rng.standard_normal((N, kv_dim), dtype=np.float32))
     v = cast(rng.standard_normal((N, kv_dim), dtype=np.float32))
 
-    def one_layer():
+    def step():
         t0 = time.perf_counter()
-        checker.append(k, v, idx.slots, kc, vc)
-        checker.paged_attention(q, kc, vc, idx.block_tables, idx.table_offset, idx.token_seq, idx.token_pos,
-                                w.q_heads, w.kv_heads, w.head_dim, bs, w.scale, threads=threads)
+        for _ in range(w.layers):
+            checker.append(k, v, idx["slots"], kc, vc)
+            checker.paged_attention(q, kc, vc, idx["block_tables"], idx["table_offset"], idx["token_seq"], idx["token_pos"],
+                                    w.q_heads, w.kv_heads, w.head_dim, bs, w.scale, threads=threads)
         return time.perf_counter() - t0
 
-    return one_layer, N
+    step.pool_gb_read_per_layer = rows.size * kv_dim * 4 * 2 / 1e9
+    return step, N
 
 
 def run_reference_arm(args, rank, world):
-    """--impl reference: the reference's CPU implementation, all host threads, bounded sample per step."""
+    """--impl reference: the reference's CPU implementation (oracle/_ref, compiled from its sources; the
+    C restatement if that is absent), all host threads, every layer of the step, --steps timed steps
+    after --warmup untimed ones.  Nothing of the product is imported or loaded."""
     if rank != 0:
         return
     import oracle
-    wl = importlib.import_module("llm-engine_b200.workloads")
+    wl = load_workloads_standalone()
     checker = oracle.load_ref()
     kind = "reference"
     if checker is None:
         checker, kind = oracle.load_orc(), "port"
     threads = oracle.ref_default_thread_count()
     w = wl.make(args.workload)
-    one_layer, N = cpu_step_sample(w, checker, threads)
-    for _ in range(max(1, min(args.warmup, 1))):
-        one_layer()
-    steps = max(1, min(args.steps, 5))
-    times = [one_layer() for _ in range(steps)]
-    t_layer = float(np.mean(times))
-    t_step = t_layer * w.layers
+    step, N = cpu_step_fn(w, checker, threads)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    t_step = (time.perf_counter() - t0) / args.steps
     value = N / t_step
-    sample = f"each step = 1 of {w.layers} layers over all {w.n_seqs} sequences (append + attention), scaled x{w.layers}; {steps} steps timed"
+    sample = f"every step = all {w.layers} layers over all {w.n_seqs} sequences (append + attention); {args.steps} steps timed after {args.warmup} warm-up steps"
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": 1, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {WORKLOAD_TEXT[args.workload]}", "device": "host CPU",
-                   "note": "the reference's CPU backend is fp32; bf16 inputs are rounded to bf16 and widened"},
+        "config": {"workload": f"{args.workload}: {WORKLOAD_TEXT[args.workload]}", "tokens_per_step_per_gpu": N, "layers": w.layers,
+                   "device": "host CPU",
+                   "note": "the reference's CPU backend is fp32; bf16 inputs are rounded to bf16 and widened; one K/V pool pair reused by "
+                           f"every layer ({step.pool_gb_read_per_layer:.2f} GB of rows read per layer)"},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -260,39 +287,59 @@ def run_ours(args, rank, local_rank, world):
     launches_per_step = (2 if fused else 3) * L      # kernels: [append,] attention, merge
 
     # ---- end-to-end step: host buffers in, host buffers out --------------------------
-    pin = lambda t: t.cpu().pin_memory()
-    h_q, h_k, h_v = pin(q), pin(k), pin(v)
+    # Host side: one pinned staging buffer per layer holding that layer's q | k | v rows back to back
+    # (one upload per layer), one for the five index arrays, the planner's own pinned staging, and one
+    # for every layer's output.  Device side: mirrors of the same shape, with contiguous q/k/v views.
+    row = H + 2 * kv_dim
+    h_qkv = torch.empty((L, N * row), dtype=tdt).pin_memory()
+    e_qkv = torch.empty((L, N * row), dtype=tdt, device=dev)
+    for l in range(L):
+        h_qkv[l, :N * H].copy_(q[l].reshape(-1))
+        h_qkv[l, N * H:N * (H + kv_dim)].copy_(k[l].reshape(-1))
+        h_qkv[l, N * (H + kv_dim):].copy_(v[l].reshape(-1))
+    e_q = [e_qkv[l, :N * H].view(N, H) for l in range(L)]
+    e_k = [e_qkv[l, N * H:N * (H + kv_dim)].view(N, kv_dim) for l in range(L)]
+    e_v = [e_qkv[l, N * (H + kv_dim):].view(N, kv_dim) for l in range(L)]
     h_out = torch.empty((L, N, H), dtype=tdt).pin_memory()
-    h_idx = [torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).pin_memory()
-             for a in (idx.slots, idx.token_seq, idx.token_pos, idx.block_tables, idx.table_offset)]
-    d_idx = [d_slots, d_seq, d_pos, d_tab, d_off]
-    e_q, e_k, e_v = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     e_out = torch.empty_like(out)
-    h2d_bytes = sum(t.numel() * t.element_size() for t in (h_q, h_k, h_v)) + sum(t.numel() * 4 for t in h_idx)
+    idx_arrays = [idx.slots, idx.token_seq, idx.token_pos, idx.block_tables, idx.table_offset]
+    idx_off = np.concatenate([[0], np.cumsum([((a.size + 63) // 64) * 64 for a in idx_arrays])])
+    h_idx = torch.zeros(int(idx_off[-1]), dtype=torch.int32).pin_memory()
+    e_idx = torch.zeros(int(idx_off[-1]), dtype=torch.int32, device=dev)
+    for a, o in zip(idx_arrays, idx_off):
+        h_idx[int(o):int(o) + a.size].copy_(torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)))
+    e_slots, e_seq, e_pos, e_tab, e_off = [e_idx[int(o):int(o) + a.size] for a, o in zip(idx_arrays, idx_off)]
+    plan_e = pkv.DecodePlan(N, w.q_heads, w.kv_heads, w.head_dim, device=dev)
+    h2d_bytes = h_qkv.numel() * h_qkv.element_size() + h_idx.numel() * 4 + plan_e.staging.numel()
     d2h_bytes = h_out.numel() * h_out.element_size()
     copy_stream = torch.cuda.Stream(device=dev)
     out_stream = torch.cuda.Stream(device=dev)
 
-    def step_e2e():
-        """Index arrays first, then layer l's q/k/v rows are uploaded on a copy stream while layer
-        l-1 computes, and layer l's output goes back while layer l+1 computes."""
+    def layer_e(l):
+        if fused:
+            plan_e.append_attention(e_q[l], e_k[l], e_v[l], e_slots, kc_l[l], vc_l[l], e_tab, e_off, e_seq, e_pos, e_out[l], bs, w.scale)
+        else:
+            pkv.launch_store_kv(e_k[l], e_v[l], e_slots, kc_l[l], vc_l[l], N, kv_dim)
+            plan_e.attention(e_q[l], kc_l[l], vc_l[l], e_tab, e_off, e_seq, e_pos, e_out[l], bs, w.scale)
+
+    def e2e_device_part():
+        """Everything of an end-to-end step that runs on the device: the index arrays and the plan image
+        go up first, layer l's q|k|v rows are uploaded on a copy stream while layer l-1 computes, and
+        layer l's output goes back while layer l+1 computes.  Capturable: no host work in here."""
         main = torch.cuda.current_stream()
-        for hs, ds in zip(h_idx, d_idx):
-            ds.copy_(hs, non_blocking=True)
-        plan.build_host(idx.token_pos)
+        e_idx.copy_(h_idx, non_blocking=True)
+        plan_e.workspace[:plan_e.staging.numel()].copy_(plan_e.staging, non_blocking=True)
         up_done = []
         copy_stream.wait_stream(main)
         with torch.cuda.stream(copy_stream):
             for l in range(L):
-                e_q[l].copy_(h_q[l], non_blocking=True)
-                e_k[l].copy_(h_k[l], non_blocking=True)
-                e_v[l].copy_(h_v[l], non_blocking=True)
+                e_qkv[l].copy_(h_qkv[l], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
                 up_done.append(ev)
         for l in range(L):
             main.wait_event(up_done[l])
-            layer(l, e_q[l], e_k[l], e_v[l], e_out[l])
+            layer_e(l)
             ev = torch.cuda.Event()
             ev.record(main)
             out_stream.wait_event(ev)
@@ -300,6 +347,20 @@ def run_ours(args, rank, local_rank, world):
                 h_out[l].copy_(e_out[l], non_blocking=True)
         main.wait_stream(out_stream)
         main.wait_stream(copy_stream)
+
+    e2e_graph = [None]
+
+    def step_e2e():
+        """One serving step as a caller of the library makes it: plan on the host from the host copy of
+        the positions (into pinned staging), then the device part -- a replay of its captured graph
+        when capture worked, eager launches otherwise -- then wait for the outputs to be in host
+        memory, as a decode loop must before it can sample."""
+        plan_e.build_host_image(idx.token_pos)
+        if e2e_graph[0] is not None:
+            e2e_graph[0].replay()
+        else:
+            e2e_device_part()
+        torch.cuda.current_stream().synchronize()
 
     def barrier():
         torch.cuda.synchronize()
@@ -396,11 +457,90 @@ def run_ours(args, rank, local_rank, world):
     # ---- end to end ---------------------------------------------------------------------
     e2e = None
     if not args.no_e2e:
+        plan_e.build_host_image(idx.token_pos)
+        e2e_device_part()                      # eager once: warms every path the capture will take
+        torch.cuda.synchronize()
+        e2e_launch = "eager launches"
+        if not args.no_graph:
+            try:
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2):
+                    e2e_device_part()
+                e2e_graph[0] = g2
+                e2e_launch = "cuda graph replay (copies are nodes of the graph)"
+            except Exception as e:
+                e2e_graph[0] = None
+                sys.stderr.write(f"[bench] capture of the end-to-end step failed, timing eager launches: {e}\n")
+                torch.cuda.synchronize()
+        h_out.zero_()
         ms_e2e = timed(step_e2e, args.steps, max(args.warmup, 3)) / args.steps
         e2e_value = tokens_all / (ms_e2e * 1e-3)
-        ok = torch.equal(e_out, out)       # same inputs through both routes: identical bits
+        ok = torch.equal(e_out, out) and torch.equal(h_out.to(dev), out)   # same inputs through both routes: identical bits, on the device and back on the host
         e2e = {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes),
-               "ms_per_step": ms_e2e, "matches_resident_output": bool(ok)}
+               "ms_per_step": ms_e2e, "matches_resident_output": bool(ok), "launch": e2e_launch,
+               "per_step": "host: split-K plan from the host positions into pinned staging; device: index arrays + plan image + one "
+                           f"q|k|v upload per layer ({L + 2} host-to-device copies), {launches_per_step} kernels, {L} device-to-host copies; "
+                           "then a stream synchronise (the outputs are needed on the host)"}
+
+    # ---- strong scaling: ONE batch of the configuration dealt over the ranks ----------------
+    # BASELINE words configuration 3 as "batch 256 ... sequence-sharded across 1/2/4/8 GPUs".  The weak
+    # line above gives every rank the whole batch; here the same batch is dealt once, longest context
+    # first to the least loaded rank (sharding.deal_sequences, "balanced"), each rank runs the step on
+    # its share out of its own pool, and the job's time is the slowest rank's.  One GPU: the deal is the
+    # whole batch, i.e. the weak measurement itself.
+    strong = None
+    if not args.no_strong:
+        if world == 1:
+            strong = {"value": value, "unit": "tok/s", "ms_per_step": ms_step, "sequences_per_rank": [N],
+                      "efficiency_vs_one_gpu": 1.0, "policy": "balanced (one rank: the whole batch)"}
+        else:
+            sel = sh.deal_sequences(w.ctx, world, rank, "balanced")
+            tabs_s = [w.tables[i] for i in sel]
+            pos_s = np.asarray([int(w.ctx[i]) for i in sel], dtype=np.int32)
+            idx_s = pkv.pack_step(tabs_s, pos_s, bs)
+            Ns = idx_s.n_tokens
+            s_slots, s_seq, s_pos = i32(idx_s.slots), i32(idx_s.token_seq), i32(idx_s.token_pos)
+            s_tab, s_off = i32(idx_s.block_tables), i32(idx_s.table_offset)
+            plan_s = pkv.DecodePlan(Ns, w.q_heads, w.kv_heads, w.head_dim, device=dev)
+            fused_s = w.dtype != "f32" and (args.append == "fused" or (args.append == "auto" and Ns * w.kv_heads < 1024))
+            qs, ks, vs, os_ = [q[l][:Ns] for l in range(L)], [k[l][:Ns] for l in range(L)], [v[l][:Ns] for l in range(L)], [out[l][:Ns] for l in range(L)]
+
+            def step_strong():
+                plan_s.build_host(idx_s.token_pos)
+                for l in range(L):
+                    if fused_s:
+                        plan_s.append_attention(qs[l], ks[l], vs[l], s_slots, kc_l[l], vc_l[l], s_tab, s_off, s_seq, s_pos, os_[l], bs, w.scale)
+                    else:
+                        pkv.launch_store_kv(ks[l], vs[l], s_slots, kc_l[l], vc_l[l], Ns, kv_dim)
+                        plan_s.attention(qs[l], kc_l[l], vc_l[l], s_tab, s_off, s_seq, s_pos, os_[l], bs, w.scale)
+
+            step_strong()
+            torch.cuda.synchronize()
+            replay_s = step_strong
+            if not args.no_graph:
+                try:
+                    gs = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gs):
+                        step_strong()
+                    replay_s = gs.replay
+                except Exception as e:
+                    sys.stderr.write(f"[bench] capture of the strong-scaling step failed, timing eager launches: {e}\n")
+                    torch.cuda.synchronize()
+            ms_s = timed(replay_s, args.steps, args.warmup) / args.steps
+            L_all = (w.ctx + w.new).astype(np.int64)
+            my_bytes = float((2 * L_all[sel] * w.kv_heads * w.head_dim * w.elem_bytes).sum())
+            gather = [None] * world
+            dist.all_gather_object(gather, (int(Ns), my_bytes))
+            strong = {"value": N / (ms_s * 1e-3), "unit": "tok/s", "ms_per_step": ms_s,
+                      "sequences_per_rank": [g_[0] for g_ in gather],
+                      "kv_bytes_per_layer_per_rank": [g_[1] for g_ in gather],
+                      "hbm_gbs_slowest_rank": max(g_[1] for g_ in gather) * L / (ms_s * 1e-3) / 1e9,
+                      "frac_of_peak_slowest_rank": max(g_[1] for g_ in gather) * L / (ms_s * 1e-3) / 1e9 / peak,
+                      "efficiency_vs_one_gpu": (ms_step / world) / ms_s,
+                      "one_gpu_ms_per_step": ms_step,
+                      "append": "inside the attention launch" if fused_s else "separate launch",
+                      "policy": "balanced: longest context first to the least loaded rank; total batch fixed at "
+                                f"{N} sequences; one-GPU time = this run's whole-batch step on one rank"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -411,11 +551,11 @@ def run_ours(args, rank, local_rank, world):
             checker, kind = oracle.load_orc(), "port"
         threads = oracle.ref_default_thread_count()
         w0 = wl.make(args.workload)
-        one_layer, n0 = cpu_step_sample(w0, checker, threads)
-        one_layer()
-        t = min(one_layer() for _ in range(3))
-        cpu = {"value": n0 / (t * w0.layers), "unit": "tok/s", "cores": threads, "kind": kind,
-               "sample": f"1 of {w0.layers} layers over all {w0.n_seqs} sequences (append + attention), best of 3, scaled x{w0.layers}"}
+        cpu_step, n0 = cpu_step_fn(w0, checker, threads)
+        cpu_step()
+        t = min(cpu_step() for _ in range(2))
+        cpu = {"value": n0 / t, "unit": "tok/s", "cores": threads, "kind": kind,
+               "sample": f"whole steps (all {w0.layers} layers over all {w0.n_seqs} sequences, append + attention), one warm-up, best of 2"}
 
     if rank == 0:
         line = {
@@ -426,12 +566,20 @@ def run_ours(args, rank, local_rank, world):
                        "layers": L, "sharding": "by sequence: each rank owns its pool and its batch, no collective",
                        "l2": f"per-step working set {algo_bytes * L / 1e9:.2f} GB across {L} distinct per-layer pools, far larger than the 126 MB L2",
                        "launch": "cuda graph replay" if use_graph else "eager launches",
+                       "plan": "split-K plan built on the host once, at capture, and its upload replayed: `value` holds no per-step host "
+                               "planning (positions change every step in serving); `e2e` re-plans on the host every step",
+                       "cpu_affinity": getattr(args, "affinity_note", None),
                        "append": "inside the attention launch (pkv_append_decode_attn_planned)" if fused else "separate launch (pkv_append)",
                        **({"layers_override": args.layers} if args.layers else {})},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "step_hbm_gbs": (algo_bytes + w.append_bytes_per_layer()) * L / (ms_step * 1e-3) / 1e9,
+            "strong": strong,
         }
+        if getattr(args, "return_line", False):
+            return line
+        if world == 1 and not args.no_secondary:
+            line["secondary"] = secondary_measurements(args, pkv, wl, torch, dev, pools, w)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -574,6 +722,8 @@ def run_prefill(args, rank, local_rank, world):
                            "l2": "24 distinct per-layer pools and q/k/v/out sets (2.4 GB per step), larger than the 126 MB L2",
                            "launch": "eager launches"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 2 * L * args.steps, "clocks": clocks}
+        if getattr(args, "return_line", False):
+            return line
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -787,17 +937,13 @@ def run_prefix_cow(args, rank, local_rank, world):
     pa = torch.from_numpy(np.asarray(pairs, dtype=np.int32)).to(dev)
     block_bytes = bs * kv_dim * 2
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 20
-    for _ in range(3):
-        pkv.launch_copy_blocks_layers(ptrs, 2 * L, pa, len(pairs), block_bytes)
+    pkv.launch_copy_blocks_layers(ptrs, 2 * L, pa, len(pairs), block_bytes)      # the workload's own copy-on-write wave
     torch.cuda.synchronize()
-    a.record()
-    for _ in range(reps):
-        pkv.launch_copy_blocks_layers(ptrs, 2 * L, pa, len(pairs), block_bytes)
-    b.record()
-    torch.cuda.synchronize()
-    cow_us = a.elapsed_time(b) / reps * 1e3
-    cow_bytes = 2 * len(pairs) * block_bytes * 2 * L          # read + write, K and V, every layer
+    # Its speed is measured on waves of the same shape over rotating disjoint pair lists: repeating the one
+    # wave (92 MB read + written) would time the 126 MB L2, not HBM.
+    import types
+    cow = measure_cow_rotated(pkv, torch, dev, pools, types.SimpleNamespace(block_size=bs, kv_dim=kv_dim, elem_bytes=2, num_blocks=nb),
+                              pairs_per_set=len(pairs))
     # suffixes (their K/V are whatever the pool holds: values do not matter for timing)
     lens = []
     for t in seqs:
@@ -874,8 +1020,7 @@ def run_prefix_cow(args, rank, local_rank, world):
             "config": {"workload": f"cfg5: {WORKLOAD_TEXT['cfg5']}", "layers": L, "launch": "eager launches, host bookkeeping in the timed region",
                        "index_build": "host (pkv_step_pack + five copies)" if args.host_pack else "device (pkv_step_pack_device, one copy)",
                        "note": "the reference never shares a partial block (docs/design.md:36); the CoW trigger is this library's additive fork()/cow()"},
-            "cow": {"pairs": len(pairs), "pools": 2 * L, "us_per_wave": cow_us, "bytes_read_plus_written": cow_bytes,
-                    "GBps": cow_bytes / cow_us / 1e3, "frac_of_measured_hbm": cow_bytes / cow_us / 1e3 / peak},
+            "cow": cow,
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_combine_kernel (whole step incl. host)",
                          "achieved": byts / steps / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": byts / steps / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src},
@@ -885,6 +1030,162 @@ def run_prefix_cow(args, rank, local_rank, world):
             "gpu_launches": 3 * L * steps}
     if rank == 0:
         print(json.dumps(line), flush=True)
+
+
+def measure_cow_rotated(pkv, torch, dev, pools, w, sets=8, pairs_per_set=127, waves=40):
+    """Copy-on-write block copy at HBM speed rather than out of L2: `sets` disjoint lists of block pairs
+    are copied in rotation over every pool of the model in one launch each, so that a block is touched
+    again only after sets x pairs x pools x 2 x block_bytes (several times the 126 MB L2) of other
+    traffic.  Pool contents are overwritten (blocks copied over blocks): call it last."""
+    L = pools.shape[0]
+    block_bytes = w.block_size * w.kv_dim * w.elem_bytes
+    ptrs = torch.tensor([pools[l, j].data_ptr() for l in range(L) for j in range(2)], dtype=torch.int64, device=dev)
+    ids = np.random.default_rng(5).permutation(w.num_blocks)[:2 * sets * pairs_per_set].astype(np.int32)
+    lists = [torch.from_numpy(np.ascontiguousarray(ids[2 * i * pairs_per_set:2 * (i + 1) * pairs_per_set].reshape(-1, 2))).to(dev)
+             for i in range(sets)]
+    wave_bytes = 2 * pairs_per_set * block_bytes * 2 * L
+    for i in range(sets):
+        pkv.launch_copy_blocks_layers(ptrs, 2 * L, lists[i], pairs_per_set, block_bytes)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(waves):
+        pkv.launch_copy_blocks_layers(ptrs, 2 * L, lists[i % sets], pairs_per_set, block_bytes)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) / waves * 1e3
+    peak, _ = peaks()
+    return {"kernel": "copy_blocks_kernel", "pairs_per_wave": pairs_per_set, "pools": 2 * L, "disjoint_pair_sets_in_rotation": sets,
+            "bytes_read_plus_written_per_wave": wave_bytes, "bytes_between_reuse_of_a_block": wave_bytes * sets,
+            "us_per_wave": us, "GBps": wave_bytes / us / 1e3, "frac_of_measured_hbm": wave_bytes / us / 1e3 / peak}
+
+
+def measure_mixed_step(pkv, torch, dev):
+    """A step as llm-engine's forward pass hands it to launch_attention_decode: two 300-token prefill chunks
+    plus 20 decode tokens (Qwen2.5-0.5B shapes, f16).  Timed per attention call: through the mixed entry
+    point (chunks routed to the tensor-core prefill kernel on the device) and through the decode entry
+    point (every chunk token a decode unit that re-reads its whole history, which is what the
+    reference's launcher does)."""
+    qh, kvh, hd, bs = 14, 2, 64, 16
+    rng = np.random.default_rng(21)
+    ctx = [1200, 700] + [int(x) for x in rng.integers(200, 3000, size=20)]
+    new = [300, 300] + [1] * 20
+    nb = sum((c + n + bs - 1) // bs for c, n in zip(ctx, new)) + 8
+    perm = rng.permutation(nb).astype(np.int32)
+    tabs, pos, at = [], [], 0
+    for c, n in zip(ctx, new):
+        kb = (c + n + bs - 1) // bs
+        t = perm[at:at + kb].copy()
+        at += kb
+        for i in range(n):
+            tabs.append(t)
+            pos.append(c + i)
+    idx = pkv.pack_step(tabs, pos, bs)
+    N = idx.n_tokens
+    f16 = lambda *shape: torch.randn(shape, device=dev, dtype=torch.float32).to(torch.float16)
+    kc, vc, q = f16(nb * bs, kvh * hd), f16(nb * bs, kvh * hd), f16(N, qh * hd)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+    d = [i32(idx.block_tables), i32(idx.table_offset), i32(idx.token_seq), i32(idx.token_pos)]
+    out_m, out_d = torch.zeros_like(q), torch.zeros_like(q)
+    ws = torch.empty(pkv.mixed_workspace_bytes(N, qh, kvh, hd), dtype=torch.uint8, device=dev)
+    scale = 1.0 / float(np.sqrt(hd))
+    mixed = lambda: pkv.launch_attention_mixed(q, kc, vc, *d, out_m, N, qh, kvh, hd, bs, scale, ws, num_blocks=nb)
+    plain = lambda: pkv.launch_attention_decode(q, kc, vc, *d, out_d, N, qh, kvh, hd, bs, scale, workspace=ws)
+    res = {}
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, fn in (("mixed_entry_point", mixed), ("decode_entry_point", plain)):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(30):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        res[name + "_us_per_call"] = a.elapsed_time(b) / 30 * 1e3
+    diff = (out_m.float() - out_d.float()).abs().max().item()
+    res.update({"step": "2 x 300-token chunks (cached 1,200 and 700) + 20 decode tokens, 14q/2kv heads, d64, f16", "tokens": N,
+                "max_abs_difference_between_the_two": diff,
+                "speedup": res["decode_entry_point_us_per_call"] / res["mixed_entry_point_us_per_call"]})
+    return res
+
+
+def run_cow(args, rank, local_rank, world):
+    """--workload cow: the block copy of configuration 5 by itself, out of HBM (rotating pair lists)."""
+    import torch
+    pkv = importlib.import_module("llm-engine_b200")
+    wl = importlib.import_module("llm-engine_b200.workloads")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    w = wl.make("cfg5", layers=args.layers or 22)
+    pools = torch.randn((w.layers, 2, w.num_blocks * w.block_size, w.kv_dim), device=dev, dtype=torch.float32).to(torch.bfloat16)
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    res = measure_cow_rotated(pkv, torch, dev, pools, w, waves=max(args.steps, 8) * 4)
+    clocks = sampler.stop()
+    if rank == 0:
+        peak, src = peaks()
+        print(json.dumps({"metric": "copy-on-write block copy GB/s (read + written)", "value": res["GBps"], "unit": "GB/s", "n_gpus": world,
+                          "steps": max(args.steps, 8) * 4, "warmup": 8, "ms_per_step": res["us_per_wave"] / 1e3, "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                          "config": {"workload": f"cow: {WORKLOAD_TEXT['cow']}", "l2": "a block is touched again only after 8 waves (733 MB) of other traffic"},
+                          "roofline": {"bound": "hbm", "kernel": "copy_blocks_kernel", "achieved": res["GBps"], "peak": peak, "unit": "GB/s",
+                                       "frac": res["GBps"] / peak, "traffic": None, "peak_source": src,
+                                       "algorithmic_bytes_per_launch": res["bytes_read_plus_written_per_wave"], "us_per_launch": res["us_per_wave"]},
+                          "cpu_baseline": None, "e2e": None, "gpu_launches": max(args.steps, 8) * 4, "clocks": clocks, "detail": res}), flush=True)
+
+
+def secondary_measurements(args, pkv, wl, torch, dev, pools, w):
+    """Short runs of the other kernels on the box the default line is measured on (one GPU only): the
+    tcgen05 prefill kernel on configuration 4's launch, the small-batch decode step of configuration 2,
+    the copy-on-write block copy out of HBM, and a mixed step through both attention entry points."""
+    import copy
+    sec = {}
+    a2 = copy.copy(args)
+    a2.return_line, a2.no_cpu, a2.no_e2e, a2.no_strong, a2.no_secondary = True, True, True, True, True
+    try:
+        a2.workload, a2.layers, a2.steps, a2.warmup = "cfg4", 4, 8, 3
+        ln = run_prefill(a2, 0, dev.index, 1)
+        r = ln["roofline"]
+        sec["cfg4_prefill"] = {"kernel": r["kernel"], "us_per_launch": r["us_per_launch"], "TFLOPs": r["achieved"], "frac_of_burst_peak": r["frac"],
+                               "frac_of_sustained_peak": r["frac_of_sustained"], "algorithmic_flops_per_launch": r["algorithmic_flops_per_launch"],
+                               "layers_run": 4, "clocks": ln["clocks"]}
+    except Exception as e:
+        sec["cfg4_prefill"] = {"error": repr(e)}
+    try:
+        a2.workload, a2.layers, a2.steps, a2.warmup = "cfg2", None, 20, 5
+        ln = run_ours(a2, 0, dev.index, 1)
+        r = ln["roofline"]
+        sec["cfg2_decode"] = {"value_tok_s": ln["value"], "ms_per_step": ln["ms_per_step"], "us_per_layer_in_graph": ln["ms_per_step"] * 1e3 / ln["config"]["layers"],
+                              "step_hbm_gbs": ln["step_hbm_gbs"], "frac_of_peak_whole_step": ln["step_hbm_gbs"] / r["peak"],
+                              "attention_us_per_launch_eager": r["us_per_launch"], "attention_frac_eager": r["frac"],
+                              "append": ln["config"]["append"], "launch": ln["config"]["launch"]}
+    except Exception as e:
+        sec["cfg2_decode"] = {"error": repr(e)}
+    try:
+        sec["mixed_step"] = measure_mixed_step(pkv, torch, dev)
+    except Exception as e:
+        sec["mixed_step"] = {"error": repr(e)}
+    try:
+        sec["cow_copy"] = measure_cow_rotated(pkv, torch, dev, pools, w)
+    except Exception as e:
+        sec["cow_copy"] = {"error": repr(e)}
+    return sec
+
+
+def bind_rank_to_cores(local_rank, world):
+    """One process per GPU on a host whose cores all sit behind one NUMA node: give every rank its own
+    slice of the cores this job may use, so that eight launch loops do not migrate over each other."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        per = len(cores) // world
+        if world > 1 and per >= 1:
+            mine = cores[local_rank * per:(local_rank + 1) * per]
+            os.sched_setaffinity(0, mine)
+            return f"rank bound to {len(mine)} of {len(cores)} cores ({mine[0]}-{mine[-1]})"
+    except Exception:
+        pass
+    return None
 
 
 def main():
@@ -904,6 +1205,8 @@ def main():
     ap.add_argument("--host-pack", action="store_true", help="cfg5: build the step indices on the host instead of on the device")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling runs only; noted in config)")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling block (one batch dealt over the ranks)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary block (prefill, small-batch decode, block copy, mixed step)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -912,6 +1215,7 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
+    args.affinity_note = bind_rank_to_cores(local_rank, world)
     if world != args.gpus:
         if args.gpus > 1 and world == 1:
             raise SystemExit("--gpus N > 1 is launched with torch.distributed.run --nproc-per-node N")
@@ -921,6 +1225,8 @@ def main():
         run_prefill(args, rank, local_rank, world)
     elif args.workload == "cfg5":
         run_prefix_cow(args, rank, local_rank, world)
+    elif args.workload == "cow":
+        run_cow(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 

@@ -38,7 +38,7 @@
 extern "C" {
 #endif
 
-#define PKV_ABI_VERSION 1
+#define PKV_ABI_VERSION 2
 
 typedef void* pkv_stream; /* a cudaStream_t */
 
@@ -58,13 +58,26 @@ const char* pkv_status_string(int status);
 /* Detail of the calling thread's most recent failure ("" if none). */
 const char* pkv_last_error(void);
 
-/* Debugging aid, the one entry point that SYNCHRONISES the device: reads and clears
- * the word in which kernels record a bounded wait that ran out (bit 0: a TMA
- * producer never saw its ring slot released; bit 1: a consumer never saw its tile
- * arrive; bit 2: a prefill pipeline wait; bit 3: a peer GPU's flag in the
- * head-sharded exchange).  0 means no kernel ever gave up.
- * No llm-engine counterpart. */
+/* Bounded waits.  Every wait inside the kernels has a limit; a wait that runs out
+ * makes its warp or block wind down (tensor memory released, no trap) and leaves the
+ * launch's output incomplete.  The record of it is a bit -- 1: a TMA producer never saw
+ * its ring slot released; 2: a consumer never saw its tile arrive; 4: a prefill
+ * pipeline wait; 8: a peer GPU's flag in the head-sharded exchange -- kept in two
+ * places: a device word, and one pinned host word the kernels store to.  The attention
+ * entry points (pkv_decode_attn_*, the planned, fused, peer and mixed forms,
+ * pkv_prefill_attn_*) look at the host word before they enqueue anything: the first
+ * such call after an incomplete launch has reached the host returns PKV_E_CUDA once,
+ * with the bits in pkv_last_error(), and enqueues nothing; the record is cleared by
+ * that report and the next call runs normally (nothing is disabled).  The three
+ * engine::launch_* symbols turn it into their std::runtime_error.
+ *
+ * pkv_debug_device_flags is the one entry point that SYNCHRONISES the device: it
+ * reads and clears both records (0: no kernel gave up).
+ * pkv_debug_set_reported_flags is a testing aid: it makes the next attention call
+ * behave as if a kernel had recorded `flags` (works without a GPU).
+ * No llm-engine counterparts. */
 int pkv_debug_device_flags(unsigned int* flags);
+int pkv_debug_set_reported_flags(unsigned int flags);
 
 /* ----------------------------------------------------------- K/V append ----
  * K/V append.  Replaces engine::launch_store_kv (include/engine/cuda_kernels.h:43-45,
@@ -180,6 +193,11 @@ typedef struct pkv_decode_plan {
   int n_items;    /* exact item count when host-built, upper bound when device-built */
   int exact;      /* 1 if n_items is exact */
   int reserved;   /* internal: bit 0 set when some token was split; the other bits count shared-prefix units */
+  int num_blocks; /* blocks in each K/V pool, or 0 if unknown.  The planners leave 0; a caller that sets it
+                     before pkv_decode_attn_planned_* gets tensor maps bounded by the pool, so that a wrong
+                     block id reads zeros instead of memory beyond it (llm-engine's launcher signature
+                     carries no pool size, which is why this is optional) */
+  int pad[3];
 } pkv_decode_plan;
 
 size_t pkv_decode_plan_staging_bytes(int n_tokens, int kv_heads);
@@ -189,6 +207,14 @@ int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int 
 int pkv_decode_plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
                            void* workspace, size_t workspace_bytes, pkv_stream stream,
                            pkv_decode_plan* plan);
+/* pkv_decode_plan_host without the copy, for a caller that replays a captured CUDA graph:
+ * the image is written to h_staging and *image_bytes says how much of it must be at the
+ * start of the workspace before the attention calls run; the caller's own graph carries
+ * that copy (a memcpy node from h_staging of any size >= *image_bytes, e.g. the whole
+ * staging buffer).  workspace_bytes is the size of the workspace the plan is for. */
+int pkv_decode_plan_host_image(const int* h_token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                               void* h_staging, size_t staging_bytes, size_t workspace_bytes,
+                               pkv_decode_plan* plan, size_t* image_bytes);
 /* Append fused into the attention: pkv_append_* followed by pkv_decode_attn_planned_*
  * in ONE kernel chain less (the two calls of src/model/cuda/cuda_model.cu:368-377
  * folded together).  The work unit that reaches a token's newest key takes that
@@ -244,6 +270,33 @@ int pkv_decode_attn_planned_f32(const pkv_decode_plan* plan, const void* q, cons
                                 const void* v_cache, const int* block_tables, const int* table_offset,
                                 const int* token_seq, const int* token_pos, void* out, int block_size,
                                 float scale, void* workspace, size_t workspace_bytes, pkv_stream stream);
+
+/* Mixed steps: prefill chunks and decode tokens in ONE call, as llm-engine's forward
+ * pass makes it (src/model/cuda/cuda_model.cu:362-377: every packed token of the step
+ * goes through launch_attention_decode; include/engine/sequence.h:74-89: prefill slices
+ * first, then decode tokens; a slice's tokens are packed consecutively,
+ * src/model/cuda/cuda_model.cu:434-447).  Arguments are those of pkv_decode_attn_* plus
+ * the pool size (num_blocks, 0 if unknown) and min_run.  On the device, with no host
+ * synchronisation, the planner finds the runs -- maximal stretches of packed tokens of
+ * one sequence at consecutive positions; runs of at least min_run tokens (<= 0: the
+ * library's default, 16) go to the tensor-core prefill kernel as (first row, length,
+ * cached context) records, all other tokens to the decode kernels, and both write the
+ * same `out`.  K/V of every token must already be in the pools (pkv_append_* first).
+ * Results agree with pkv_decode_attn_* on the same step within the dtype's tolerance.
+ * Steps shorter than min_run, a null workspace, and geometries the prefill kernel does
+ * not run (head_dim other than 64, block_size not a power of two >= 16) take the
+ * pkv_decode_attn_* path unchanged.  The workspace holds the split-K scratch and the
+ * router's arrays: at least pkv_mixed_attn_workspace_bytes(...), 256-byte aligned.
+ * engine::launch_attention_decode[_gqa] as exported by this library call this. */
+size_t pkv_mixed_attn_workspace_bytes(int n_tokens, int q_heads, int kv_heads, int head_dim);
+int pkv_mixed_attn_f16(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                       const int* table_offset, const int* token_seq, const int* token_pos, void* out,
+                       int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks,
+                       float scale, int min_run, void* workspace, size_t workspace_bytes, pkv_stream stream);
+int pkv_mixed_attn_bf16(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                        const int* table_offset, const int* token_seq, const int* token_pos, void* out,
+                        int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks,
+                        float scale, int min_run, void* workspace, size_t workspace_bytes, pkv_stream stream);
 
 /* -------------------------------------------------- head-sharded decode ----
  * Head-sharded decode over the GPUs of one box (one process per GPU).  The path
@@ -307,9 +360,12 @@ int pkv_peer_free(void* ptr);
  * caller's chunk size, include/engine/scheduler.h:26).  bf16 and f16, head_dim 64,
  * block_size a power of two >= 16, q_heads % kv_heads == 0; other geometries return
  * PKV_E_UNSUPPORTED (such steps go through pkv_decode_attn_*, as in the reference).
- * The kernel is persistent and hands its work out through a ticket counter taken
- * from a pool of 64 inside the library: at most 64 prefill launches may be in
- * flight on one GPU at a time (streams included). */
+ * The kernel is persistent.  Eager launches hand their work out through a ticket
+ * counter that belongs to (device, stream): calls on one stream never share it in
+ * time, calls on different streams never share it at all, so any number may overlap.
+ * A call made during stream capture, or on the 65th distinct stream of a device,
+ * deals its work in a fixed order instead and touches no shared counter, so a
+ * captured graph may be replayed next to anything. */
 int pkv_prefill_attn_bf16(const void* q, const void* k_cache, const void* v_cache,
                           const int* block_tables, const int* table_offset, const int* q_start,
                           const int* q_len, const int* ctx_len, void* out, int n_tokens, int n_seqs,

@@ -24,7 +24,8 @@ class PkvError(RuntimeError):
 class DecodePlan(C.Structure):
     """Mirror of struct pkv_decode_plan."""
     _fields_ = [("n_tokens", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int), ("head_dim", C.c_int),
-                ("chunk", C.c_int), ("n_items", C.c_int), ("exact", C.c_int), ("reserved", C.c_int)]
+                ("chunk", C.c_int), ("n_items", C.c_int), ("exact", C.c_int), ("reserved", C.c_int),
+                ("num_blocks", C.c_int), ("pad", C.c_int * 3)]
 
 
 _vp, _i, _f, _sz, _u64 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_uint64
@@ -35,6 +36,9 @@ SIGNATURES = {
     "pkv_status_string": (C.c_char_p, [_i]),
     "pkv_last_error": (C.c_char_p, []),
     "pkv_debug_device_flags": (_i, [_vp]),
+    "pkv_debug_set_reported_flags": (_i, [C.c_uint]),
+    "pkv_mixed_attn_workspace_bytes": (_sz, [_i] * 4),
+    **{f"pkv_mixed_attn_{s}": (_i, [_vp] * 8 + [_i] * 6 + [_f, _i, _vp, _sz, _vp]) for s in ("f16", "bf16")},
     **{f"pkv_append_{s}": (_i, [_vp] * 5 + [_i, _i, _vp]) for s in ("f16", "bf16", "f32")},
     **{f"pkv_rope_append_{s}": (_i, [_vp] * 9 + [_i] * 4 + [_vp]) for s in ("f16", "bf16", "f32")},
     "pkv_decode_workspace_bytes": (_sz, [_i] * 4),
@@ -42,6 +46,7 @@ SIGNATURES = {
     "pkv_decode_attn_bf16_builtin_scratch": (_i, [_vp] * 8 + [_i] * 5 + [_f, _vp]),
     "pkv_decode_plan_staging_bytes": (_sz, [_i, _i]),
     "pkv_decode_plan_host": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
+    "pkv_decode_plan_host_image": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _sz, C.POINTER(DecodePlan), C.POINTER(_sz)]),
     "pkv_decode_plan_device": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp, C.POINTER(DecodePlan)]),
     **{f"pkv_decode_attn_planned_peer_{s}": (_i, [C.POINTER(DecodePlan)] + [_vp] * 7 + [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp])
        for s in ("f16", "bf16")},

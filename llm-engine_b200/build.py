@@ -24,6 +24,7 @@ SOURCES = [
     "rope_append.cu",
     "step_pack.cu",
     "peer_memory.cu",
+    "error_mirror.cu",
     "decode_attn.cu",
     "prefill_attn.cu",
     "engine_shim.cu",

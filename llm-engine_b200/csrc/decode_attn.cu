@@ -20,6 +20,14 @@ static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratch
 
 namespace pkv {
 int prefill_read_flags(unsigned int* flags);  // prefill_attn.cu
+template <typename T>
+int prefill_launch(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                   const int* table_offset, const int* q_start, const int* q_len, const int* ctx_len, void* out,
+                   int n_tokens, int n_seqs, int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
+                   int num_blocks, float scale, pkv_stream stream, const int* d_dims, bool may_allocate);
+unsigned int* error_mirror(bool create);      // error_mirror.cu
+unsigned int take_error_mirror();
+int check_error_mirror(const char* fn);
 namespace {
 
 // ---- tuning knobs (read once) ---------------------------------------------------
@@ -56,16 +64,138 @@ int max_extra(int kv_heads) { return (tuning().max_extra_cap + kv_heads - 1) / k
 // One block builds the whole work list from the device copy of token_pos.
 constexpr int kPlanThreads = 1024;
 
+// Mixed-step routing (optional first phase of the planner).  llm-engine's forward pass sends a
+// whole step through one attention call: prefill slices first, then decode tokens, a slice's tokens
+// packed consecutively (src/model/cuda/cuda_model.cu:362-377, 434-447; include/engine/sequence.h:74-89).
+// A run is a maximal stretch of packed tokens of one sequence at consecutive positions.  Runs of at
+// least min_run tokens are prefill chunks: they get a (first row, length, cached context, table
+// offset) record for the tensor-core prefill kernel and their tokens an effective length of 0,
+// which takes them out of the decode plan; every other token keeps position + 1.
+struct RouteArgs {
+  const int* token_seq;
+  const int* table_offset;
+  int min_run, q_heads;
+  int* run_start;   // [n_tokens] scratch: first token of the run a token belongs to
+  int* run_len;     // [n_tokens] scratch: length of a run, stored at its first token
+  int* eff_len;     // [n_tokens] out
+  int* q_start;     // [n_tokens / min_run + 1] out, and the three below
+  int* q_len;
+  int* ctx_len;
+  int* tbl_off;
+  int* dims;        // [4] out: runs, 128-row tiles of the longest run, prefill work items, decode tokens
+};
+
+__device__ void route_phase(const int* __restrict__ token_pos, int n, const RouteArgs& r, int* sm_scan, int* sm_misc) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  auto is_start = [&](int t) {
+    return t == 0 || r.token_seq[t] != r.token_seq[t - 1] || token_pos[t] != token_pos[t - 1] + 1;
+  };
+  // 1. running maximum of the start indices = first token of each token's run
+  int carry = 0;
+  for (int base = 0; base < n; base += kPlanThreads) {
+    const int t = base + tid;
+    int v = (t < n && is_start(t)) ? t : -1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v = max(v, x);
+    }
+    if (lane == 31) sm_scan[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      int a = sm_scan[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(0xffffffffu, a, o);
+        if (lane >= o) a = max(a, x);
+      }
+      sm_scan[lane] = a;
+    }
+    __syncthreads();
+    v = max(v, max(warp ? sm_scan[warp - 1] : -1, carry));
+    if (t < n) r.run_start[t] = v;
+    carry = max(carry, sm_scan[kPlanThreads / 32 - 1]);
+    __syncthreads();
+  }
+  // 2. the last token of a run stores the run's length at its first token
+  for (int t = tid; t < n; t += kPlanThreads) {
+    if (t == n - 1 || is_start(t + 1)) {
+      const int rs = r.run_start[t];
+      r.run_len[rs] = t - rs + 1;
+    }
+  }
+  if (tid == 0) { sm_misc[0] = 0; sm_misc[1] = 0; sm_misc[2] = 0; }   // runs so far, longest run, decode tokens
+  __syncthreads();
+  // 3. effective lengths and the records of the long runs, in packed order
+  for (int base = 0; base < n; base += kPlanThreads) {
+    const int t = base + tid;
+    int flag = 0, len = 0;
+    if (t < n) {
+      const int rs = r.run_start[t];
+      len = r.run_len[rs];
+      const bool long_run = len >= r.min_run;
+      r.eff_len[t] = long_run ? 0 : max(token_pos[t], 0) + 1;
+      flag = (long_run && rs == t) ? 1 : 0;
+      if (!long_run) atomicAdd(&sm_misc[2], 1);
+    }
+    int sc = flag;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, sc, o);
+      if (lane >= o) sc += x;
+    }
+    if (lane == 31) sm_scan[warp] = sc;
+    __syncthreads();
+    if (warp == 0) {
+      int a = sm_scan[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(0xffffffffu, a, o);
+        if (lane >= o) a += x;
+      }
+      sm_scan[lane] = a;
+    }
+    __syncthreads();
+    if (flag) {
+      const int i = sm_misc[0] + (warp ? sm_scan[warp - 1] : 0) + sc - 1;
+      r.q_start[i] = t;
+      r.q_len[i] = len;
+      r.ctx_len[i] = max(token_pos[t], 0);
+      r.tbl_off[i] = r.table_offset[r.token_seq[t]];
+      atomicMax(&sm_misc[1], len);
+    }
+    __syncthreads();
+    if (tid == 0) sm_misc[0] += sm_scan[kPlanThreads / 32 - 1];
+    __syncthreads();
+  }
+  if (tid == 0) {
+    const int tiles = (sm_misc[1] + 127) / 128;
+    r.dims[0] = sm_misc[0];
+    r.dims[1] = tiles;
+    r.dims[2] = sm_misc[0] * tiles * r.q_heads;
+    r.dims[3] = sm_misc[2];
+  }
+  __syncthreads();
+}
+
+template <bool ROUTE>
 __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int* __restrict__ token_pos, int n_tokens,
                                                                     int kv_heads, long long extra_budget,
                                                                     int wave_ctas, int forced_chunk,
                                                                     PlanHeader* header, TokSplit* tok_split,
-                                                                    int* counters, WorkItem* items) {
+                                                                    int* counters, WorkItem* items, const RouteArgs route) {
   __shared__ unsigned long long sm_items[kNumChunkCandidates];
   __shared__ int sm_chunk;
   __shared__ int sm_scan_items[kPlanThreads / 32], sm_scan_parts[kPlanThreads / 32];
   __shared__ int sm_carry_items, sm_carry_parts;
+  __shared__ int sm_misc[4];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if constexpr (ROUTE) route_phase(token_pos, n_tokens, route, sm_scan_items, sm_misc);
+  // keys the decode path handles for token t: position + 1, or 0 for a token the router gave to the prefill kernel
+  auto length_of = [&](int t) {
+    if constexpr (ROUTE) return route.eff_len[t];
+    return max(token_pos[t], 0) + 1;
+  };
   if (tid < kNumChunkCandidates) sm_items[tid] = 0ull;
   if (tid == 0) { sm_carry_items = 0; sm_carry_parts = 0; }
   __syncthreads();
@@ -74,7 +204,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int* __
 #pragma unroll
     for (int j = 0; j < kNumChunkCandidates; ++j) loc[j] = 0ull;
     for (int t = tid; t < n_tokens; t += kPlanThreads) {
-      const int L = max(token_pos[t], 0) + 1;
+      const int L = length_of(t);
 #pragma unroll
       for (int j = 0; j < kNumChunkCandidates; ++j) loc[j] += static_cast<unsigned>((L + (kMinChunk << j) - 1) / (kMinChunk << j));
     }
@@ -98,8 +228,8 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int* __
     const int t = base + tid;
     int L = 0, ns = 0;
     if (t < n_tokens) {
-      L = max(token_pos[t], 0) + 1;
-      ns = chunk > 0 ? (L + chunk - 1) / chunk : 1;
+      L = length_of(t);
+      ns = L == 0 ? 0 : (chunk > 0 ? (L + chunk - 1) / chunk : 1);
     }
     const int np = ns > 1 ? ns : 0;
     // inclusive scans of ns and np across the block
@@ -200,9 +330,9 @@ int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
   alignas(64) CUtensorMap kmap, vmap;
   constexpr bool is_bf16 = !std::is_same<T, __half>::value;
   const int kv_dim = a.kv_heads * a.head_dim;
-  int st = make_pool_tensor_map(&kmap, a.k_cache, is_bf16, kv_dim, 16, 1ull << 30);
+  int st = make_pool_tensor_map(&kmap, a.k_cache, is_bf16, kv_dim, 16, a.pool_rows);
   if (st != PKV_OK) return st;
-  st = make_pool_tensor_map(&vmap, a.v_cache, is_bf16, kv_dim, 16, 1ull << 30);
+  st = make_pool_tensor_map(&vmap, a.v_cache, is_bf16, kv_dim, 16, a.pool_rows);
   if (st != PKV_OK) return st;
   // `grid` counts work units; every warp is a worker and blocks are persistent:
   // as many as can be resident, each warp striding through the unit list.
@@ -363,6 +493,8 @@ void fill_args(DecodeArgs& a, const void* q, const void* kc, const void* vc, con
   for (int p = 0; p < kMaxPeers; ++p) { a.peer_out[p] = nullptr; a.peer_flags[p] = nullptr; }
   a.n_peers = 0; a.my_rank = 0; a.epoch = 0;
   a.new_k = nullptr; a.new_v = nullptr; a.slots = nullptr;
+  a.host_err = nullptr;
+  a.pool_rows = 1ull << 30;
 }
 
 void attach_workspace(DecodeArgs& a, void* workspace, const WsLayout& w) {
@@ -397,18 +529,25 @@ int plan_budget(int n_tokens, int q_heads, int kv_heads, int head_dim, size_t wo
 }
 
 int plan_device(const int* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim, void* workspace,
-                size_t workspace_bytes, cudaStream_t stream, pkv_decode_plan* plan) {
+                size_t workspace_bytes, cudaStream_t stream, pkv_decode_plan* plan, const RouteArgs* route = nullptr) {
   if (!token_pos || !workspace || !plan) return fail(PKV_E_ARG, "pkv_decode_plan_device: null pointer");
+  std::memset(plan, 0, sizeof(*plan));
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PKV_E_ARG, "pkv_decode_plan_device: workspace must be 256-byte aligned");
   WsLayout w;
   const int budget = plan_budget(n_tokens, q_heads, kv_heads, head_dim, workspace_bytes, &w);
   if (budget < 0)
     return fail(PKV_E_WORKSPACE, "pkv_decode_plan_device: workspace of %zu bytes cannot hold the plan for %d tokens", workspace_bytes, n_tokens);
   char* base = static_cast<char*>(workspace);
-  decode_plan_kernel<<<1, kPlanThreads, 0, stream>>>(
-      token_pos, n_tokens, kv_heads, budget, tuning().wave_ctas, tuning().forced_chunk,
-      reinterpret_cast<PlanHeader*>(base), reinterpret_cast<TokSplit*>(base + w.off_tok),
-      reinterpret_cast<int*>(base + w.off_cnt), reinterpret_cast<WorkItem*>(base + w.off_items));
+  if (route)
+    decode_plan_kernel<true><<<1, kPlanThreads, 0, stream>>>(
+        token_pos, n_tokens, kv_heads, budget, tuning().wave_ctas, tuning().forced_chunk,
+        reinterpret_cast<PlanHeader*>(base), reinterpret_cast<TokSplit*>(base + w.off_tok),
+        reinterpret_cast<int*>(base + w.off_cnt), reinterpret_cast<WorkItem*>(base + w.off_items), *route);
+  else
+    decode_plan_kernel<false><<<1, kPlanThreads, 0, stream>>>(
+        token_pos, n_tokens, kv_heads, budget, tuning().wave_ctas, tuning().forced_chunk,
+        reinterpret_cast<PlanHeader*>(base), reinterpret_cast<TokSplit*>(base + w.off_tok),
+        reinterpret_cast<int*>(base + w.off_cnt), reinterpret_cast<WorkItem*>(base + w.off_items), RouteArgs{});
   int st = check_launch("decode_plan_kernel");
   if (st != PKV_OK) return st;
   plan->n_tokens = n_tokens; plan->q_heads = q_heads; plan->kv_heads = kv_heads; plan->head_dim = head_dim;
@@ -435,11 +574,13 @@ template <typename T>
 int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, const void* vc, const int* bt,
                    const int* to, const int* ts, const int* tp, void* out, int block_size, float scale,
                    void* workspace, size_t workspace_bytes, pkv_stream stream, const PeerSetup* peers = nullptr,
-                   const FusedAppend* app = nullptr) {
+                   const FusedAppend* app = nullptr, bool may_allocate = true) {
   const char* fn = peers ? "pkv_decode_attn_planned_peer" : (app ? "pkv_append_decode_attn_planned" : "pkv_decode_attn_planned");
   if (!plan) return fail(PKV_E_ARG, "%s: null plan", fn);
   if (plan->n_tokens <= 0) return PKV_OK;
-  int st = validate_geometry(fn, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size);
+  int st = check_error_mirror(fn);
+  if (st != PKV_OK) return st;
+  st = validate_geometry(fn, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size);
   if (st != PKV_OK) return st;
   st = validate_pointers(fn, q, kc, vc, bt, to, ts, tp, out, sizeof(T) * static_cast<size_t>(plan->head_dim));
   if (st != PKV_OK) return st;
@@ -450,6 +591,8 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
   DecodeArgs a;
   fill_args(a, q, kc, vc, bt, to, ts, tp, out, plan->n_tokens, plan->q_heads, plan->kv_heads, plan->head_dim, block_size, scale);
   attach_workspace(a, workspace, w);
+  a.host_err = error_mirror(may_allocate);
+  if (plan->num_blocks > 0) a.pool_rows = static_cast<unsigned long long>(plan->num_blocks) * block_size;
   if (peers) {
     if constexpr (sizeof(T) != 2) return fail(PKV_E_UNSUPPORTED, "%s: the head-sharded exchange is for 16-bit outputs", fn);
     if (peers->n_peers < 1 || peers->n_peers > kMaxPeers || peers->my_rank < 0 || peers->my_rank >= peers->n_peers)
@@ -494,16 +637,20 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
 template <typename T>
 int decode_all_in_one(const void* q, const void* kc, const void* vc, const int* bt, const int* to, const int* ts,
                       const int* tp, void* out, int n_tokens, int q_heads, int kv_heads, int head_dim,
-                      int block_size, float scale, void* workspace, size_t workspace_bytes, pkv_stream stream) {
+                      int block_size, float scale, void* workspace, size_t workspace_bytes, pkv_stream stream,
+                      bool may_allocate = true) {
   const char* fn = "pkv_decode_attn";
   if (n_tokens <= 0 || q_heads <= 0) return PKV_OK;  // the reference launchers' silent no-op
-  int st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, block_size);
+  int st = check_error_mirror(fn);
+  if (st != PKV_OK) return st;
+  st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, block_size);
   if (st != PKV_OK) return st;
   st = validate_pointers(fn, q, kc, vc, bt, to, ts, tp, out, sizeof(T) * static_cast<size_t>(head_dim));
   if (st != PKV_OK) return st;
   if (!workspace) {
     DecodeArgs a;
     fill_args(a, q, kc, vc, bt, to, ts, tp, out, n_tokens, q_heads, kv_heads, head_dim, block_size, scale);
+    a.host_err = error_mirror(may_allocate);
     long long blocks = static_cast<long long>(n_tokens) * kv_heads;
     if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
     return launch_decode<T>(a, static_cast<int>(blocks), static_cast<cudaStream_t>(stream), false);
@@ -511,7 +658,83 @@ int decode_all_in_one(const void* q, const void* kc, const void* vc, const int* 
   pkv_decode_plan plan;
   st = plan_device(tp, n_tokens, q_heads, kv_heads, head_dim, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), &plan);
   if (st != PKV_OK) return st;
-  return decode_planned<T>(&plan, q, kc, vc, bt, to, ts, tp, out, block_size, scale, workspace, workspace_bytes, stream);
+  return decode_planned<T>(&plan, q, kc, vc, bt, to, ts, tp, out, block_size, scale, workspace, workspace_bytes, stream,
+                           nullptr, nullptr, may_allocate);
+}
+
+// ---- mixed steps ------------------------------------------------------------------------
+int default_min_run() {
+  static const int v = [] { const int e = env_int("PKV_MIXED_MIN_RUN", 16); return e < 1 ? 1 : e; }();
+  return v;
+}
+
+// Router scratch behind the decode workspace: three int arrays of n_tokens, four of max_runs, the counts.
+struct RouteLayout { size_t off_start, off_len, off_eff, off_qs, off_ql, off_ctx, off_tbl, off_dims, total; };
+RouteLayout route_layout(int n_tokens) {
+  RouteLayout r;
+  const size_t arr = align256(sizeof(int) * static_cast<size_t>(n_tokens));
+  r.off_start = 0; r.off_len = arr; r.off_eff = 2 * arr;
+  r.off_qs = 3 * arr; r.off_ql = 4 * arr; r.off_ctx = 5 * arr; r.off_tbl = 6 * arr;
+  r.off_dims = 7 * arr;
+  r.total = 7 * arr + 256;
+  return r;
+}
+
+template <typename T>
+bool prefill_capable(int head_dim, int block_size, float scale) {
+  if constexpr (IsF32<T>::value) return false;
+  return head_dim == 64 && log2_exact(block_size) >= 4 && scale > 0.f && tensor_map_encoder() != nullptr;
+}
+
+template <typename T>
+int mixed_attn(const void* q, const void* kc, const void* vc, const int* bt, const int* to, const int* ts, const int* tp,
+               void* out, int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks,
+               float scale, int min_run, void* workspace, size_t workspace_bytes, pkv_stream stream) {
+  const char* fn = "pkv_mixed_attn";
+  if (n_tokens <= 0 || q_heads <= 0) return PKV_OK;
+  if (min_run <= 0) min_run = default_min_run();
+  // Steps that cannot hold a prefill chunk, and geometries the prefill kernel does not run, are plain decode steps.
+  if (n_tokens < min_run || !workspace || !prefill_capable<T>(head_dim, block_size, scale))
+    return decode_all_in_one<T>(q, kc, vc, bt, to, ts, tp, out, n_tokens, q_heads, kv_heads, head_dim, block_size, scale,
+                                workspace, workspace_bytes, stream);
+  int st = check_error_mirror(fn);
+  if (st != PKV_OK) return st;
+  st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, block_size);
+  if (st != PKV_OK) return st;
+  st = validate_pointers(fn, q, kc, vc, bt, to, ts, tp, out, sizeof(T) * static_cast<size_t>(head_dim));
+  if (st != PKV_OK) return st;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PKV_E_ARG, "%s: workspace must be 256-byte aligned", fn);
+  const RouteLayout rl = route_layout(n_tokens);
+  if (workspace_bytes < rl.total + ws_layout(n_tokens, q_heads, kv_heads, head_dim, 0).total)
+    return fail(PKV_E_WORKSPACE, "%s: workspace of %zu bytes is too small for a step of %d tokens (pkv_mixed_attn_workspace_bytes)",
+                fn, workspace_bytes, n_tokens);
+  const size_t dec_bytes = (workspace_bytes - rl.total) & ~static_cast<size_t>(255);
+  char* rbase = static_cast<char*>(workspace) + dec_bytes;
+  RouteArgs r;
+  r.token_seq = ts; r.table_offset = to;
+  r.min_run = min_run; r.q_heads = q_heads;
+  r.run_start = reinterpret_cast<int*>(rbase + rl.off_start);
+  r.run_len = reinterpret_cast<int*>(rbase + rl.off_len);
+  r.eff_len = reinterpret_cast<int*>(rbase + rl.off_eff);
+  r.q_start = reinterpret_cast<int*>(rbase + rl.off_qs);
+  r.q_len = reinterpret_cast<int*>(rbase + rl.off_ql);
+  r.ctx_len = reinterpret_cast<int*>(rbase + rl.off_ctx);
+  r.tbl_off = reinterpret_cast<int*>(rbase + rl.off_tbl);
+  r.dims = reinterpret_cast<int*>(rbase + rl.off_dims);
+  pkv_decode_plan plan;
+  std::memset(&plan, 0, sizeof(plan));
+  st = plan_device(tp, n_tokens, q_heads, kv_heads, head_dim, workspace, dec_bytes, static_cast<cudaStream_t>(stream), &plan, &r);
+  if (st != PKV_OK) return st;
+  plan.num_blocks = num_blocks > 0 ? num_blocks : 0;
+  // decode tokens (and short runs) through the decode kernels; tokens of long runs are in no work item
+  st = decode_planned<T>(&plan, q, kc, vc, bt, to, ts, tp, out, block_size, scale, workspace, dec_bytes, stream);
+  if (st != PKV_OK) return st;
+  // the long runs through the tensor-core kernel, whose item counts come from the router
+  const int max_runs = n_tokens / min_run;
+  if constexpr (!IsF32<T>::value)
+    st = prefill_launch<T>(q, kc, vc, bt, r.tbl_off, r.q_start, r.q_len, r.ctx_len, out, n_tokens, max_runs, n_tokens,
+                           q_heads, kv_heads, head_dim, block_size, num_blocks, scale, stream, r.dims, true);
+  return st;
 }
 
 }  // namespace
@@ -530,7 +753,7 @@ int pkv_debug_device_flags(unsigned int* flags) {
   unsigned int pf = 0;
   const int st = pkv::prefill_read_flags(&pf);
   if (st != PKV_OK) return st;
-  *flags = v | pf;
+  *flags = v | pf | pkv::take_error_mirror();
   return PKV_OK;
 }
 
@@ -545,17 +768,17 @@ size_t pkv_decode_plan_staging_bytes(int n_tokens, int kv_heads) {
   return w.off_ml;  // header .. end of items
 }
 
-int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
-                         void* h_staging, size_t staging_bytes, void* workspace, size_t workspace_bytes,
-                         pkv_stream stream, pkv_decode_plan* plan) {
-  const char* fn = "pkv_decode_plan_host";
+// Builds the plan image in host memory; *image_bytes is what has to reach the start of the workspace.
+static int plan_host_image(const char* fn, const int* h_token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                           void* h_staging, size_t staging_bytes, size_t workspace_bytes, pkv_decode_plan* plan,
+                           size_t* image_bytes) {
   if (!plan) return fail(PKV_E_ARG, "%s: null plan", fn);
   std::memset(plan, 0, sizeof(*plan));
+  *image_bytes = 0;
   if (n_tokens <= 0) return PKV_OK;
-  if (!h_token_pos || !h_staging || !workspace) return fail(PKV_E_ARG, "%s: null pointer", fn);
+  if (!h_token_pos || !h_staging) return fail(PKV_E_ARG, "%s: null pointer", fn);
   int st = validate_geometry(fn, n_tokens, q_heads, kv_heads, head_dim, 1);
   if (st != PKV_OK) return st;
-  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PKV_E_ARG, "%s: workspace must be 256-byte aligned", fn);
   WsLayout w;
   const int budget = plan_budget(n_tokens, q_heads, kv_heads, head_dim, workspace_bytes, &w);
   if (budget < 0) return fail(PKV_E_WORKSPACE, "%s: workspace of %zu bytes cannot hold the plan for %d tokens", fn, workspace_bytes, n_tokens);
@@ -610,14 +833,36 @@ int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int 
   hd->n_tokens = n_tokens;
   hd->n_parts = np;
   hd->kv_heads = kv_heads;
-  cudaError_t e = cudaMemcpyAsync(workspace, img, image, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: plan upload failed: %s", fn, cudaGetErrorString(e));
+  *image_bytes = image;
   plan->n_tokens = n_tokens; plan->q_heads = q_heads; plan->kv_heads = kv_heads; plan->head_dim = head_dim;
   plan->chunk = chunk;
   plan->n_items = ni;
   plan->exact = 1;
   plan->reserved = np > 0 ? 1 : 0;       // whether any token was split (the merge kernel is skipped otherwise)
   return PKV_OK;
+}
+
+int pkv_decode_plan_host(const int* h_token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                         void* h_staging, size_t staging_bytes, void* workspace, size_t workspace_bytes,
+                         pkv_stream stream, pkv_decode_plan* plan) {
+  const char* fn = "pkv_decode_plan_host";
+  if (n_tokens > 0 && !workspace) return fail(PKV_E_ARG, "%s: null pointer", fn);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PKV_E_ARG, "%s: workspace must be 256-byte aligned", fn);
+  size_t image = 0;
+  const int st = plan_host_image(fn, h_token_pos, n_tokens, q_heads, kv_heads, head_dim, h_staging, staging_bytes,
+                                 workspace_bytes, plan, &image);
+  if (st != PKV_OK || image == 0) return st;
+  const cudaError_t e = cudaMemcpyAsync(workspace, h_staging, image, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: plan upload failed: %s", fn, cudaGetErrorString(e));
+  return PKV_OK;
+}
+
+int pkv_decode_plan_host_image(const int* h_token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                               void* h_staging, size_t staging_bytes, size_t workspace_bytes, pkv_decode_plan* plan,
+                               size_t* image_bytes) {
+  if (!image_bytes) return fail(PKV_E_ARG, "pkv_decode_plan_host_image: null image_bytes");
+  return plan_host_image("pkv_decode_plan_host_image", h_token_pos, n_tokens, q_heads, kv_heads, head_dim, h_staging,
+                         staging_bytes, workspace_bytes, plan, image_bytes);
 }
 
 int pkv_decode_plan_host_shared(const int* h_token_pos, const int* h_token_seq, const int* h_tables,
@@ -838,9 +1083,10 @@ int pkv_decode_attn_bf16_builtin_scratch(const void* q, const void* k_cache, con
   void* ws = nullptr;
   st = builtin_scratch_address(&ws);
   if (st != PKV_OK) return st;
+  // may_allocate = false: the pinned word that mirrors give-ups is used only if another call created it
   return decode_all_in_one<__nv_bfloat16>(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,
                                           n_tokens, q_heads, kv_heads, head_dim, block_size, scale, ws,
-                                          kBuiltinScratchBytes, stream);
+                                          kBuiltinScratchBytes, stream, false);
 }
 
 #define PKV_DECODE_ENTRY(SUFFIX, TYPE)                                                                               \
@@ -895,5 +1141,23 @@ PKV_DECODE_PEER_ENTRY(bf16, __nv_bfloat16)
 
 PKV_APPEND_DECODE_ENTRY(f16, __half)
 PKV_APPEND_DECODE_ENTRY(bf16, __nv_bfloat16)
+
+size_t pkv_mixed_attn_workspace_bytes(int n_tokens, int q_heads, int kv_heads, int head_dim) {
+  if (n_tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0) return 0;
+  return pkv_decode_workspace_bytes(n_tokens, q_heads, kv_heads, head_dim) + route_layout(n_tokens).total;
+}
+
+#define PKV_MIXED_ENTRY(SUFFIX, TYPE)                                                                                \
+  int pkv_mixed_attn_##SUFFIX(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,      \
+                              const int* table_offset, const int* token_seq, const int* token_pos, void* out,       \
+                              int n_tokens, int q_heads, int kv_heads, int head_dim, int block_size, int num_blocks, \
+                              float scale, int min_run, void* workspace, size_t workspace_bytes, pkv_stream stream) { \
+    return mixed_attn<TYPE>(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out, n_tokens,    \
+                            q_heads, kv_heads, head_dim, block_size, num_blocks, scale, min_run, workspace,          \
+                            workspace_bytes, stream);                                                                \
+  }
+
+PKV_MIXED_ENTRY(f16, __half)
+PKV_MIXED_ENTRY(bf16, __nv_bfloat16)
 
 }  // extern "C"

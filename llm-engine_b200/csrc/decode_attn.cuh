@@ -72,7 +72,19 @@ struct DecodeArgs {
   const void* new_k;
   const void* new_v;
   const int* slots;
+  unsigned int* host_err;   // pinned host word that also receives a give-up (null: none)
+  unsigned long long pool_rows;   // slots the K/V tensor maps cover (the pool size when the caller gave it, else a bound)
 };
+
+// Records a bounded wait that ran out: in the device word, and in the host's pinned word if the
+// launch was given one, so that the caller's next call can report it without synchronising.
+__device__ __forceinline__ void report_give_up(const DecodeArgs& a, unsigned int bit) {
+  atomicOr(&g_pkv_device_error, bit);
+  if (a.host_err) {
+    *reinterpret_cast<volatile unsigned int*>(a.host_err) = bit;
+    __threadfence_system();
+  }
+}
 
 // Output row of (token, head 0) under the layout above.
 template <typename T>
@@ -309,7 +321,7 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];\n" : "=r"(seen) : "l"(mine + p) : "memory");
             if (seen - epoch >= 0) break;
             if (++spins > (1u << 23)) {                      // about two seconds: the peer is not coming
-              atomicOr(&g_pkv_device_error, kErrPeerWait);
+              report_give_up(a, kErrPeerWait);
               break;
             }
             __nanosleep(200);

@@ -24,8 +24,10 @@
 //           other writes its split-K partial, fire and forget; decode_combine_kernel
 //           (decode_attn.cuh) merges the partials afterwards.
 //
-// Every mbarrier wait is bounded; a wait that runs out records a flag in
-// g_pkv_device_error and the warp winds down instead of spinning.
+// Every mbarrier wait is bounded; a wait that runs out records a flag (device word and the
+// host's pinned word) and the warp winds down instead of spinning.  Blocks are persistent and all
+// start together, so a launch ends within a few wait limits whatever happens; a recorded flag
+// does not stop later launches.
 #pragma once
 
 #include "decode_attn.cuh"
@@ -82,10 +84,6 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   unsigned char* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
   const uint32_t bars = smem_u32(&full_bar[warp * NSTAGES]);
   const float sl2 = a.scale * kLog2e;
-
-  // Once any warp has given up on a wait, later blocks do not start: the launch
-  // then ends within one wait limit instead of one per block.
-  if (*reinterpret_cast<volatile unsigned int*>(&g_pkv_device_error) != 0u) return;
 
   if (lane == 0) {
 #pragma unroll
@@ -233,7 +231,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
       while (more && n_issued - n_consumed < NSTAGES) more = issue_next();
       const uint32_t slot = n_consumed % NSTAGES;
       if (!mbar_wait(bars + 8 * slot, (n_consumed / NSTAGES) & 1u)) {
-        if (lane == 0) atomicOr(&g_pkv_device_error, kErrConsumerWait);
+        if (lane == 0) report_give_up(a, kErrConsumerWait);
         ok = false;
         break;
       }

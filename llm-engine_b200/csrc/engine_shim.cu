@@ -13,12 +13,23 @@
 // (src/kernels/attention_decode.cu:147-154, attention_decode_gqa.cu:211-224), and
 // nothing here synchronises the device.
 //
-// The reference signatures carry no workspace argument, so split-K scratch is
-// kept here in a grow-only device buffer per GPU -- the same pattern as the
-// caller's own Scratch<T> buffers (src/model/cuda/cuda_model.cu:212-233).  It is
-// (re)allocated only when a step needs more than any step before it, which is the
-// one moment this file calls cudaMalloc.  Set PKV_SHIM_NO_WORKSPACE=1 to run
-// without it (no split-K).
+// Every packed token of a step comes through launch_attention_decode, prefill chunks
+// included (src/model/cuda/cuda_model.cu:362-377).  The launchers hand the step to
+// pkv_mixed_attn_f16, which finds the chunks on the device and sends them to the
+// tensor-core prefill kernel and everything else to the decode kernels; geometries the
+// prefill kernel does not run take the decode path, as before.
+//
+// The reference signatures carry no workspace argument, so split-K and router scratch
+// is kept here in a grow-only device buffer per GPU -- the same pattern as the
+// caller's own Scratch<T> buffers (src/model/cuda/cuda_model.cu:212-233).  A larger
+// buffer is allocated when a step needs more than any step before it, which is the
+// one moment this file calls cudaMalloc (so: not during stream capture, where
+// allocation is illegal; size the first step generously or warm up before capturing).
+// Buffers that were outgrown are kept until the process exits rather than freed: work
+// already enqueued may still use them, and cudaFree would wait for the device.  One
+// buffer per device serves every stream: calls on different streams of one device
+// must not overlap, as with the caller's own single-stream scratch.  Set
+// PKV_SHIM_NO_WORKSPACE=1 to run without scratch (no split-K, no prefill routing).
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -26,6 +37,7 @@
 #include <mutex>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "pkv.h"
 
@@ -34,6 +46,7 @@ namespace {
 struct DeviceScratch {
   void* ptr = nullptr;
   size_t bytes = 0;
+  std::vector<void*> outgrown;
 };
 constexpr int kMaxDevices = 64;
 DeviceScratch g_scratch[kMaxDevices];
@@ -48,16 +61,16 @@ void* scratch_for(size_t need, size_t* have) {
   std::lock_guard<std::mutex> lock(g_mu);
   DeviceScratch& s = g_scratch[dev];
   if (s.bytes < need) {
-    // Work already enqueued may still read the old buffer: cudaFree waits for it.
-    if (s.ptr) cudaFree(s.ptr);
-    s.ptr = nullptr;
-    s.bytes = 0;
     const size_t grown = need + need / 2;
-    if (cudaMalloc(&s.ptr, grown) != cudaSuccess) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, grown) != cudaSuccess) {
       cudaGetLastError();
-      s.ptr = nullptr;
-      return nullptr;  // fall back to the unsplit path rather than fail the step
+      if (s.bytes == 0) return nullptr;   // no scratch at all: the unsplit path rather than a failed step
+      *have = s.bytes;                    // keep using the smaller buffer: the call sizes its plan to it
+      return s.ptr;
     }
+    if (s.ptr) s.outgrown.push_back(s.ptr);
+    s.ptr = p;
     s.bytes = grown;
   }
   *have = s.bytes;
@@ -73,9 +86,13 @@ void decode(const char* fn, const __half* q, const __half* k_cache, const __half
             int q_heads, int kv_heads, int head_dim, int block_size, float scale, cudaStream_t stream) {
   if (n_tokens <= 0 || q_heads <= 0 || kv_heads <= 0) return;
   size_t have = 0;
-  void* ws = scratch_for(pkv_decode_workspace_bytes(n_tokens, q_heads, kv_heads, head_dim), &have);
-  const int st = pkv_decode_attn_f16(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,
-                                     n_tokens, q_heads, kv_heads, head_dim, block_size, scale, ws, have, stream);
+  void* ws = scratch_for(pkv_mixed_attn_workspace_bytes(n_tokens, q_heads, kv_heads, head_dim), &have);
+  int st = pkv_mixed_attn_f16(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out, n_tokens,
+                              q_heads, kv_heads, head_dim, block_size, /*num_blocks=*/0, scale, /*min_run=*/0, ws, have,
+                              stream);
+  if (st == PKV_E_WORKSPACE)   // an outgrown buffer that could not be replaced: still correct without the router
+    st = pkv_decode_attn_f16(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out, n_tokens,
+                             q_heads, kv_heads, head_dim, block_size, scale, ws, have, stream);
   if (st != PKV_OK) raise(fn, st);
 }
 

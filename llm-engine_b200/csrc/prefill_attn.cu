@@ -9,8 +9,11 @@
 // memory.  The result it must agree with is ref::paged_attention_head
 // (include/engine/ops.h:87-111) applied to every (token, head) of the chunk.
 //
-// Thread blocks are persistent, two per SM: each takes items from a ticket counter
-// until none are left, and its roles run ahead of one another across items (the next
+// Thread blocks are persistent, two per SM: each takes items until none are left --
+// from a ticket counter that belongs to the launch's stream, or, where no counter can
+// be handed out safely (stream capture, more streams than counters), in a fixed
+// serpentine deal of the length-ranked list -- and its roles run ahead of one another
+// across items (the next
 // item's Q and first K/V tiles are fetched, and its first scores computed, while the
 // softmax warps still write the current item's output), which hides the 4,000-cycle
 // start of an item (look-ups through the block table, first loads, first MMA) and the
@@ -41,7 +44,8 @@
 // Every mbarrier wait is bounded: a wait that runs out sets bit 2 of the device error
 // word and the block carries on to its tear-down (tensor memory is always released).
 #include <algorithm>
-#include <atomic>
+#include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -53,8 +57,12 @@ namespace pkv {
 
 __device__ unsigned int g_pkv_prefill_error = 0;
 
-// Ticket and completion counters of the persistent kernel, one pair per launch in flight (the host
-// hands out slots round-robin); the last block of a launch leaves its pair at zero.
+// Ticket and completion counters of the persistent kernel, one pair per (device, stream): launches
+// on one stream never overlap between their first ticket and their last (stream order; a
+// programmatically launched successor takes its first ticket only after griddepcontrol.wait), and
+// the last block of a launch leaves its pair at zero.  Launches that cannot be tied to a stream
+// that way (stream capture: the graph may be replayed anywhere; more live streams than pairs) use
+// no counter at all: their blocks take items in a fixed order.
 constexpr int kTicketSlots = 64;
 __device__ unsigned int g_prefill_ticket[kTicketSlots];
 __device__ unsigned int g_prefill_done[kTicketSlots];
@@ -64,17 +72,16 @@ namespace {
 constexpr int kQTile = 128;     // query rows per block
 constexpr int kKTile = 64;      // keys per tile
 constexpr int kHd = 64;         // head_dim this kernel is written for
-constexpr int kThreads = 192;
 constexpr int kKVStages = 4;
 constexpr int kBox = 16 * 128;                   // one TMA box: 16 slots x 128 bytes
 constexpr int kQBytes = kQTile * 128;            // 128 rows x 128 bytes
 constexpr int kKBytes = kKTile * 128;            // one K (or V, or P) tile: 64 keys x 128 bytes / 128 rows x 64 keys
 constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kSmemQ + 2 * kQBytes;                // two Q tiles (this item's and the next), then kKVStages x (K, V)
-constexpr int kSmemOnes = kSmemKV + kKVStages * 2 * kKBytes; // a V-shaped tile of 1.0: P x ones = row sums
-constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 105 KB: two blocks per SM
+constexpr int kSmemTotal = kSmemKV + kKVStages * 2 * kKBytes + 1024;   // 97 KB: two blocks per SM
+constexpr int kThreads = 192, kProducerWarp = 4, kMmaWarp = 5;
 constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
-constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64) with the row sums right behind (16)
+constexpr uint32_t kTmemS = 0, kTmemP = 128, kTmemO = 192;   // S0 @0, S1 @64 (fp32 scores), P0 @128, P1 @160 (16-bit pairs), O @192 (64)
 constexpr int kMaxRanked = 256;       // launches of up to this many (sequence, tile) groups hand them out longest first
 constexpr float kRescaleThreshold = 8.f;                     // in log2 units: P stays below 2^8
 
@@ -89,9 +96,15 @@ struct PrefillArgs {
   int block_size, bs_log2;
   float scale;
   // persistent scheduling: items = sequences x query-tile slots x heads, handed out by a ticket counter
+  // (ticket == nullptr: dealt in a fixed order instead)
   unsigned int* ticket;
   unsigned int* done;
   int n_items, n_qtiles_max, n_seqs;
+  // When non-null, { n_seqs, n_qtiles_max, n_items } are read from this device array instead (written
+  // by an earlier kernel on the stream: the mixed-step router decides on the device which runs of
+  // tokens are prefill chunks); the three fields above are then upper bounds that sized the grid.
+  const int* dims;
+  unsigned int* host_err;   // pinned host word that also receives a give-up (null: none)
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
@@ -121,6 +134,13 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -180,6 +200,40 @@ __device__ __forceinline__ void ffma2(float a0, float a1, float s, float n, floa
       : "f"(a0), "f"(a1), "f"(s), "f"(n));
 }
 
+// Packed add: (a0, a1) += (b0, b1) in one instruction.
+__device__ __forceinline__ void fadd2(float& a0, float& a1, float b0, float b1) {
+  asm("{\n .reg .b64 ra, rb;\n mov.b64 ra, {%0, %1};\n mov.b64 rb, {%2, %3};\n add.rn.f32x2 ra, ra, rb;\n mov.b64 {%0, %1}, ra;\n}\n"
+      : "+f"(a0), "+f"(a1)
+      : "f"(b0), "f"(b1));
+}
+
+// Packed fused multiply-add with vector operands: (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1).
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+
+// 2^x for a pair, on the FMA and integer pipes instead of the exponential unit: n = round(x) by the
+// magic-number addition, f = x - n in [-0.5, 0.5], 2^f by a cubic (relative error 7.5e-5, well inside
+// what a 16-bit P keeps), then n added into the exponent field.  x is clamped at -126 first, which
+// also turns the -inf of a masked score into a denormal-sized weight (2^-126) instead of garbage.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& e0, float& e1) {
+  constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  float t0, t1, n0, n1, f0, f1, p0, p1;
+  fma2(t0, t1, x0, x1, 1.f, 1.f, kMagic, kMagic);
+  fma2(n0, n1, t0, t1, 1.f, 1.f, -kMagic, -kMagic);
+  fma2(f0, f1, n0, n1, -1.f, -1.f, x0, x1);
+  fma2(p0, p1, f0, f1, 0.0551716685f, 0.0551716685f, 0.2426111251f, 0.2426111251f);
+  fma2(p0, p1, p0, p1, f0, f1, 0.6932609677f, 0.6932609677f);
+  fma2(p0, p1, p0, p1, f0, f1, 0.9999280572f, 0.9999280572f);
+  e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 // Three-input maximum: one instruction on this architecture.
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -187,7 +241,13 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-__device__ __forceinline__ void give_up() { atomicOr(&g_pkv_prefill_error, 4u); }
+__device__ __forceinline__ void give_up(unsigned int* host_err) {
+  atomicOr(&g_pkv_prefill_error, 4u);
+  if (host_err) {
+    *reinterpret_cast<volatile unsigned int*>(host_err) = 4u;
+    __threadfence_system();
+  }
+}
 
 // What the TMA producer publishes about the work item it has fetched; the other roles read it
 // from shared memory once the item's Q tile barrier has completed.
@@ -197,33 +257,36 @@ struct ItemDesc {
   int pad[2];
 };
 
-template <typename T>
+// POLY: of every four pairs of scores, how many take their exponentials from ex2_poly2 instead of
+// the exponential unit (0, 1 or 2).
+template <typename T, int POLY>
 __global__ void __launch_bounds__(kThreads, 2)
     prefill_tc_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap qmap,
                       const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr uint32_t kIdescQK = instr_desc(kBf16, kKTile, false);
-  constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd + 16, true);   // 64 output dims + 16 row-sum columns
+  constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd, true);
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[4 + 2 * kKVStages + 6];
+  __shared__ __align__(8) unsigned long long bars[4 + 2 * kKVStages + 8];
   __shared__ __align__(16) ItemDesc s_item[2];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sOnes = base + kSmemOnes;
+  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = KV_FULL + kKVStages, S_FULL = KV_EMPTY + kKVStages, P_FULL = S_FULL + 2, PV_DONE = P_FULL + 2 };
+  enum { Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = KV_FULL + kKVStages, S_FULL = KV_EMPTY + kKVStages,
+         S_READ = S_FULL + 2, P_FULL = S_READ + 2, PV_DONE = P_FULL + 2 };
 
   // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(BAR(Q_FULL + i), 1);
-      mbar_init(BAR(Q_EMPTY + i), 1 + 128);   // tcgen05.commit after the item's last Q K^T, and every softmax thread once it has read the item
+      mbar_init(BAR(Q_EMPTY + i), 1 + 128);   // tcgen05.commit after the item's last Q K^T, and every softmax thread once it is done with the item
     }
     for (int i = 0; i < kKVStages; ++i) {
       mbar_init(BAR(KV_FULL + i), 1);
@@ -231,20 +294,13 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(BAR(S_FULL + i), 1);     // tcgen05.commit after Q K_j^T
-      mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P
-      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated
+      mbar_init(BAR(S_READ + i), 128);   // every softmax thread, once its row of S_j is in registers
+      mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P_j
+      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated, P_j consumed
     }
     mbar_fence_init();
   }
-  if (threadIdx.x < kKTile) {
-    // the tile of ones that makes columns 64..79 of every P V product the row sums of P
-    const uint32_t one2 = pack2<T>(1.f, 1.f);
-    unsigned char* orow = base_ptr + kSmemOnes + threadIdx.x * 128;
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(orow + ch * 16) = make_uint4(one2, one2, one2, one2);
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-  }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -263,11 +319,14 @@ __global__ void __launch_bounds__(kThreads, 2)
   // natural order, whose tail matters less the more items there are.
   __shared__ int s_key[kMaxRanked];
   __shared__ short s_order[kMaxRanked];
-  const int n_groups = a.n_seqs * a.n_qtiles_max;
+  const int n_seqs = a.dims ? __ldcg(a.dims) : a.n_seqs;
+  const int n_qtiles_max = a.dims ? __ldcg(a.dims + 1) : a.n_qtiles_max;
+  const int n_items = a.dims ? __ldcg(a.dims + 2) : a.n_items;
+  const int n_groups = n_seqs * n_qtiles_max;
   const bool ranked = n_groups <= kMaxRanked;
   if (ranked) {
     for (int j = threadIdx.x; j < n_groups; j += kThreads) {
-      const int z = j / a.n_qtiles_max, y = j - z * a.n_qtiles_max;
+      const int z = j / n_qtiles_max, y = j - z * n_qtiles_max;
       const int ql = __ldg(a.q_len + z);
       const int nt = (ql + kQTile - 1) / kQTile;
       s_key[j] = y < nt ? __ldg(a.ctx_len + z) + min((nt - y) * kQTile, ql) : -1;   // keys that tile sees; -1: no such tile
@@ -285,26 +344,28 @@ __global__ void __launch_bounds__(kThreads, 2)
     __syncthreads();
   }
 
-  // The block is persistent: it takes (sequence, query tile, head) items from a ticket counter until
-  // none are left.  Every role runs its own loop over the items and keeps its own running counts of
-  // items (n) and key tiles (g), from which ring stages, buffers and barrier parities follow; the
-  // roles are coupled only through the barriers, so the producer prefetches the next item's Q and
-  // first K/V tiles, and the MMA thread computes its first scores, while the softmax warps are
-  // still writing the current item's output.
-  // After a wait has run out (here or in an earlier block of this launch) no further wait spins:
-  // the block falls through its schedule and releases its tensor memory.
-  bool dead = *reinterpret_cast<volatile unsigned int*>(&g_pkv_prefill_error) != 0u;
+  // The block is persistent: it takes (sequence, query tile, head) items until none are left.  Every
+  // role runs its own loop over the items and keeps its own running counts of items (n) and key tiles
+  // (g), from which ring stages, buffers and barrier parities follow; the roles are coupled only
+  // through the barriers, so the producer prefetches the next item's Q and first K/V tiles, and the
+  // MMA thread computes its first scores, while the softmax warps are still writing the current
+  // item's output.
+  // After one of this thread's waits has run out no further wait of its spins: the block falls
+  // through its schedule and releases its tensor memory.  (The record of a give-up does not stop
+  // later launches: each launch stands on its own.)
+  bool dead = false;
   auto WAIT = [&](uint32_t bar, uint32_t parity) {
     if (dead) return;
     if (!mbar_wait(bar, parity)) {
       dead = true;
-      give_up();
+      give_up(a.host_err);
     }
   };
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ================================ TMA producer ================================
     int n = 0, g = 0;
+    unsigned round = 0;                                        // fixed deal: items taken so far
     for (;;) {
       dead = __shfl_sync(0xffffffffu, dead ? 1 : 0, 0) != 0;   // only lane 0 waits: keep the warp in step
       // next item that has work: heads fastest (the heads of a group share their K/V tiles through
@@ -315,14 +376,21 @@ __global__ void __launch_bounds__(kThreads, 2)
       d.n_kt = -1;
       while (!dead) {
         unsigned t = 0;
-        if (lane == 0) t = atomicAdd(a.ticket, 1u);
-        t = __shfl_sync(0xffffffffu, t, 0);
-        if (t >= static_cast<unsigned>(a.n_items)) break;
+        if (a.ticket != nullptr) {
+          if (lane == 0) t = atomicAdd(a.ticket, 1u);
+          t = __shfl_sync(0xffffffffu, t, 0);
+        } else {
+          // serpentine deal of the (length-ranked) list: block b takes place b of every even round and
+          // place G - 1 - b of every odd one, so that no block collects the longest item of every round
+          t = round * gridDim.x + ((round & 1u) ? gridDim.x - 1u - blockIdx.x : blockIdx.x);
+          ++round;
+        }
+        if (t >= static_cast<unsigned>(n_items)) break;
         const int head = static_cast<int>(t % a.q_heads);
         int rest = static_cast<int>(t / a.q_heads);
         if (ranked) rest = s_order[rest];
-        const int slot_y = rest % a.n_qtiles_max;
-        seq = rest / a.n_qtiles_max;
+        const int slot_y = rest % n_qtiles_max;
+        seq = rest / n_qtiles_max;
         const int q_len = __ldg(a.q_len + seq);
         const int tile = (q_len + kQTile - 1) / kQTile - 1 - slot_y;
         if (tile < 0) continue;
@@ -381,33 +449,38 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
       ++n;
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ================================
     // One thread issues everything.  A tcgen05.mma returns to the issuing thread at the rate the
     // tensor pipe retires them (48 cycles for 128 x 64 x 16 from shared memory, 45 with A in tensor
     // memory), a blocking try_wait costs a few hundred cycles even on a completed phase (mbar_wait
     // looks first), and the scalar code of a lone thread runs at one dependent instruction every
-    // few cycles, so the schedule is kept to two waits, eight MMAs and three commits per key tile:
-    //  * no separate "S buffer free" barrier: a softmax thread has read S_{g-1} and written P_{g-1}
-    //    over it before it arrives on P_FULL_{g-1}; this thread waits for that, issues P_{g-1} V_{g-1},
-    //    and only then S_{g+1} into the same buffer (instructions of one thread execute in order);
-    //  * O += P V and the row sums of P come out of ONE MMA of N = 80: the B operand is MN-major,
-    //    its first 64 columns are the V tile and its next column block, one leading-dimension
-    //    offset away, is a tile of ones.
+    // few cycles, so the schedule is kept to three waits, eight MMAs and three commits per key tile.
+    // Scores run TWO tiles ahead of the softmax warps: S_{g+2} goes into the buffer of S_g as soon
+    // as every softmax thread has S_g in registers (S_READ), which is early in its work on tile g,
+    // because P has buffers of its own and does not overwrite the scores it came from.  While the
+    // softmax warps work on tile g, S_{g+1} is complete and S_{g+2} is in the pipe, so they never
+    // wait for scores in steady state, and the pipe's queue (shared with the SM's other block) is
+    // off their critical path.  Then O += P_g V_g once P_g is there (A operand from tensor memory,
+    // B the V tile as MN-major operand).
     // It does not wait for the softmax warps' epilogue: after an item's last P V it goes on to the
     // next item's first scores.
     if (lane == 0) {
       const uint64_t desc_q0 = smem_desc(sQ), desc_k0 = smem_desc(sKV);
-      int n = 0, g = 0;
+      int n = 0, g = 0;       // g: key tiles whose P V has been issued (all items)
+      int gq = 0;             // key tiles whose Q K^T has been issued
       while (!dead) {
         const int qb = n & 1;
         WAIT(BAR(Q_FULL + qb), (n >> 1) & 1);
         const int n_kt = s_item[qb].n_kt;
         if (n_kt <= 0 || dead) break;
         const uint64_t desc_q = desc_q0 + ((qb * kQBytes) >> 4);
-        auto issue_qk = [&](int gg, bool last_of_item) {
-          const int st = gg % kKVStages, sb = gg & 1;
-          WAIT(BAR(KV_FULL + st), (gg / kKVStages) & 1);
+        const int g_end = g + n_kt;          // first tile of the next item
+        auto issue_qk = [&]() {
+          // scores of tile gq into buffer gq & 1, whose previous tenant (tile gq - 2) must have been read
+          const int st = gq % kKVStages, sb = gq & 1;
+          if (gq >= 2) WAIT(BAR(S_READ + sb), ((gq - 2) >> 1) & 1);
+          WAIT(BAR(KV_FULL + st), (gq / kKVStages) & 1);
           tc_fence_after();
           // descriptors differ only in their 14-bit start-address field: add to the low word
           const uint64_t kd = desc_k0 + ((st * 2 * kKBytes) >> 4);
@@ -415,17 +488,18 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int ks = 0; ks < kHd / 16; ++ks)
             tc_mma(tmem + kTmemS + sb * 64, desc_q + 2 * ks, kd + 2 * ks, kIdescQK, ks > 0);
           tc_commit(BAR(S_FULL + sb));
-          if (last_of_item) tc_commit(BAR(Q_EMPTY + qb));      // the Q tile has been read for the last time
+          ++gq;
+          if (gq == g_end) tc_commit(BAR(Q_EMPTY + qb));      // the Q tile has been read for the last time
         };
-        issue_qk(g, n_kt == 1);
+        issue_qk();
+        if (gq < g_end) issue_qk();
         for (int j = 0; j < n_kt; ++j, ++g) {
           const int st = g % kKVStages, sb = g & 1;
-          if (j + 1 < n_kt) issue_qk(g + 1, j + 2 == n_kt);
+          if (gq < g_end) issue_qk();                            // tile g + 2 (waits for S_g to have been read)
           WAIT(BAR(P_FULL + sb), (g >> 1) & 1);
           tc_fence_after();
-          const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
-          const uint64_t vd = smem_desc(v_base, sOnes - v_base);
-          const uint32_t p_addr = tmem + kTmemS + sb * 64;      // P lies over the first 32 columns of its S buffer
+          const uint64_t vd = smem_desc(sKV + st * 2 * kKBytes + kKBytes);
+          const uint32_t p_addr = tmem + kTmemP + sb * 32;
 #pragma unroll
           for (int kk = 0; kk < kKTile / 16; ++kk)
             tc_mma_ts(tmem + kTmemO, p_addr + kk * 8, vd + kk * (kBox >> 4), kIdescPV, (j | kk) != 0);
@@ -449,10 +523,11 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (d.n_kt <= 0 || dead) break;
       const int n_kt = d.n_kt, kv_total = d.kv_total, rows_here = d.rows_here;
       const int limit = d.limit0 + min(r, rows_here - 1);   // last visible key position of this row
-      // Reference maximum of the row.  It follows the true running maximum lazily: O and the row
-      // sum stay in tensor memory and are only rescaled when the maximum has grown by more than
-      // 2^8, so most tiles cost no read-modify-write of the accumulator at all.
+      // Reference maximum of the row.  It follows the true running maximum lazily: O stays in tensor
+      // memory and is only rescaled (with the row sum, which lives in this thread) when the maximum
+      // has grown by more than 2^8, so most tiles cost no read-modify-write of the accumulator.
       float m_used = -INFINITY;
+      float l_acc[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // row sum of P, four chains of packed pairs
 
       for (int j = 0; j < n_kt; ++j, ++g) {
         const int sb = g & 1;
@@ -471,6 +546,9 @@ __global__ void __launch_bounds__(kThreads, 2)
             sc[32 + i] = __uint_as_float(v1[i]);
           }
         }
+        // the scores are in registers: their buffer may take the scores of the tile after next
+        tc_fence_before();
+        mbar_arrive(BAR(S_READ + sb));
         // Causal mask, only on tiles that reach past some row's last visible key (warp-uniform test).
         if (__any_sync(0xffffffffu, k0 + kKTile - 1 > limit)) {
 #pragma unroll
@@ -489,8 +567,8 @@ __global__ void __launch_bounds__(kThreads, 2)
         if (j == 0) {
           m_used = mx;                                 // finite: key 0 is visible to every row
         } else if (__any_sync(0xffffffffu, (mx - m_used) * sl2 > kRescaleThreshold)) {
-          // Rare: bring this warp's rows of O and of the row sums to the new maximum.  Each thread
-          // owns its own tensor-memory lane; the previous tile's P V must have landed and this tile's
+          // Rare: bring this warp's rows of O and their row sums to the new maximum.  Each thread owns
+          // its own tensor-memory lane; the previous tile's P V must have landed and this tile's
           // cannot start before this thread has arrived on P_FULL below.
           WAIT(BAR(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1);
           tc_fence_after();
@@ -498,7 +576,9 @@ __global__ void __launch_bounds__(kThreads, 2)
           const float f = ex2_approx((m_used - m_new) * sl2);
           m_used = m_new;
 #pragma unroll
-          for (int blk = 0; blk < 3; ++blk) {          // O: columns 128..191, row sums: 192..223
+          for (int c = 0; c < 4; ++c) { l_acc[c][0] *= f; l_acc[c][1] *= f; }
+#pragma unroll
+          for (int blk = 0; blk < kHd / 32; ++blk) {
             uint32_t v[32];
             tc_ld32(tmem + lane_addr + kTmemO + blk * 32, v);
             tc_wait_ld();
@@ -508,9 +588,9 @@ __global__ void __launch_bounds__(kThreads, 2)
           }
         }
         const float neg = -m_used * sl2;
-        // P goes back into tensor memory as packed 16-bit pairs over the first 32 columns of the S
-        // buffer it came from: this thread has all of its own row in registers, and the MMA thread
-        // overwrites the buffer with the scores after next only after it has issued this P V.
+        // P_g goes to its own buffer in tensor memory as packed 16-bit pairs (32 columns), which the
+        // P V of tile g - 2 must have finished reading; that was issued two tiles ago.
+        if (g >= 2) WAIT(BAR(PV_DONE + sb), ((g - 2) >> 1) & 1);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
@@ -518,9 +598,17 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
             ffma2(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1], sl2, neg, x0, x1);
-            pk[i] = pack2<T>(ex2_approx(x0), ex2_approx(x1));
+            float e0, e1;
+            if ((i & 3) < POLY) {
+              ex2_poly2(x0, x1, e0, e1);
+            } else {
+              e0 = ex2_approx(x0);
+              e1 = ex2_approx(x1);
+            }
+            fadd2(l_acc[i & 3][0], l_acc[i & 3][1], e0, e1);
+            pk[i] = pack2<T>(e0, e1);
           }
-          tc_st16(tmem + lane_addr + kTmemS + sb * 64 + c * 16, pk);
+          tc_st16(tmem + lane_addr + kTmemP + sb * 32 + c * 16, pk);
         }
         if (j == n_kt - 1 && kv_total - k0 < kKTile) {
           // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
@@ -543,10 +631,9 @@ __global__ void __launch_bounds__(kThreads, 2)
       WAIT(BAR(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1);
       tc_fence_after();
       {
-        uint32_t o0[32], o1[32], lv[32];
+        uint32_t o0[32], o1[32];
         tc_ld32(tmem + lane_addr + kTmemO, o0);
         tc_ld32(tmem + lane_addr + kTmemO + 32, o1);
-        tc_ld32(tmem + lane_addr + kTmemL, lv);
         tc_wait_ld();
         tc_fence_before();
         // The row goes through shared memory so that the global stores are whole 128-byte lines
@@ -554,7 +641,8 @@ __global__ void __launch_bounds__(kThreads, 2)
         // area is the item's own Q tile, which nothing reads any more (the item's last Q K^T has
         // completed); each warp stages and drains its own 32 rows, 16-byte pieces XOR-swizzled
         // against bank conflicts.
-        const float inv = 1.f / __uint_as_float(lv[0]);
+        const float l = (l_acc[0][0] + l_acc[0][1]) + (l_acc[1][0] + l_acc[1][1]) + ((l_acc[2][0] + l_acc[2][1]) + (l_acc[3][0] + l_acc[3][1]));
+        const float inv = 1.f / l;
         unsigned char* stage = base_ptr + kSmemQ + qb * kQBytes;
         unsigned char* my_row = stage + r * 128;
 #pragma unroll
@@ -590,12 +678,12 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
-  // The last block out resets the ticket counter for the next launch that uses this slot.
-  if (threadIdx.x == 0) {
+  // The last block out resets the ticket counter for the next launch on this stream.
+  if (threadIdx.x == 0 && a.ticket != nullptr) {
     __threadfence();
     if (atomicAdd(a.done, 1u) == gridDim.x - 1) {
       *a.ticket = 0u;
@@ -612,17 +700,67 @@ int log2_exact(int x) {
   return l;
 }
 
+// The ticket pair of (current device, stream), or null when none can be handed out safely: the
+// stream is capturing (the graph could be replayed on any stream, next to anything), the table of
+// pairs is full, or PKV_PREFILL_SCHED=static asks for the fixed deal.
+struct TicketPair { unsigned int* ticket; unsigned int* done; };
+TicketPair ticket_pair_for(cudaStream_t stream, int dev) {
+  static const bool force_static = [] { const char* e = std::getenv("PKV_PREFILL_SCHED"); return e && e[0] == 's'; }();
+  TicketPair none{nullptr, nullptr};
+  if (force_static || dev < 0 || dev >= 64) return none;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { cudaGetLastError(); return none; }
+  if (cap != cudaStreamCaptureStatusNone) return none;
+  struct PerDevice {
+    unsigned int* ticket_base = nullptr;
+    unsigned int* done_base = nullptr;
+    cudaStream_t streams[kTicketSlots];
+    int n = 0;
+  };
+  static PerDevice table[64];
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  PerDevice& d = table[dev];
+  if (!d.ticket_base) {
+    void *t = nullptr, *dn = nullptr;
+    if (cudaGetSymbolAddress(&t, g_prefill_ticket) != cudaSuccess || cudaGetSymbolAddress(&dn, g_prefill_done) != cudaSuccess) {
+      cudaGetLastError();
+      return none;
+    }
+    d.ticket_base = static_cast<unsigned int*>(t);
+    d.done_base = static_cast<unsigned int*>(dn);
+  }
+  int slot = -1;
+  for (int i = 0; i < d.n; ++i)
+    if (d.streams[i] == stream) { slot = i; break; }
+  if (slot < 0) {
+    if (d.n >= kTicketSlots) return none;
+    slot = d.n++;
+    d.streams[slot] = stream;
+  }
+  return TicketPair{d.ticket_base + slot, d.done_base + slot};
+}
+
+}  // namespace
+
+unsigned int* error_mirror(bool create);                 // error_mirror.cu
+int check_error_mirror(const char* fn);
+
+// Shared by the C entry points below and by the mixed-step router (decode_attn.cu).  With d_dims the
+// per-sequence arrays and their counts come from an earlier kernel on the stream: n_seqs and
+// max_q_len are then upper bounds that size the grid, and table_offset is indexed like q_start.
+// num_blocks <= 0: the pool size is unknown (llm-engine's launcher signature carries none).
 template <typename T>
-int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
-                 const int* table_offset, const int* q_start, const int* q_len, const int* ctx_len, void* out,
-                 int n_tokens, int n_seqs, int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
-                 int num_blocks, float scale, pkv_stream stream) {
+int prefill_launch(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                   const int* table_offset, const int* q_start, const int* q_len, const int* ctx_len, void* out,
+                   int n_tokens, int n_seqs, int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
+                   int num_blocks, float scale, pkv_stream stream, const int* d_dims, bool may_allocate) {
   const char* fn = "pkv_prefill_attn";
   if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return PKV_OK;
   if (!q || !k_cache || !v_cache || !block_tables || !table_offset || !q_start || !q_len || !ctx_len || !out)
     return fail(PKV_E_ARG, "%s: null device pointer", fn);
-  if (q_heads <= 0 || kv_heads <= 0 || num_blocks <= 0)
-    return fail(PKV_E_ARG, "%s: q_heads %d, kv_heads %d, num_blocks %d must be > 0", fn, q_heads, kv_heads, num_blocks);
+  if (q_heads <= 0 || kv_heads <= 0)
+    return fail(PKV_E_ARG, "%s: q_heads %d and kv_heads %d must be > 0", fn, q_heads, kv_heads);
   if (q_heads % kv_heads != 0)
     return fail(PKV_E_UNSUPPORTED, "%s: q_heads %d is not a multiple of kv_heads %d", fn, q_heads, kv_heads);
   if (head_dim != kHd)
@@ -640,20 +778,25 @@ int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const 
   constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
   alignas(64) CUtensorMap qmap, kmap, vmap;
   const int kv_dim = kv_heads * head_dim;
-  int st = make_pool_tensor_map(&kmap, k_cache, is_bf16, kv_dim, 16, static_cast<uint64_t>(num_blocks) * block_size);
+  const uint64_t pool_rows = num_blocks > 0 ? static_cast<uint64_t>(num_blocks) * block_size : (1ull << 30);
+  int st = make_pool_tensor_map(&kmap, k_cache, is_bf16, kv_dim, 16, pool_rows);
   if (st != PKV_OK) return st;
-  st = make_pool_tensor_map(&vmap, v_cache, is_bf16, kv_dim, 16, static_cast<uint64_t>(num_blocks) * block_size);
+  st = make_pool_tensor_map(&vmap, v_cache, is_bf16, kv_dim, 16, pool_rows);
   if (st != PKV_OK) return st;
   // q as [n_tokens][q_heads*head_dim]; rows past n_tokens read as zeros
   st = make_pool_tensor_map(&qmap, q, is_bf16, q_heads * head_dim, kQTile, static_cast<uint64_t>(n_tokens));
   if (st != PKV_OK) return st;
 
-  auto kern = prefill_tc_kernel<T>;
+  // PKV_PREFILL_POLY = 0 | 1 | 2: share (in quarters) of the exponentials computed on the FMA pipe.
+  static const int poly = [] { const char* e = std::getenv("PKV_PREFILL_POLY"); return (e && *e >= '0' && *e <= '2') ? *e - '0' : 0; }();
+  auto kern = poly == 2 ? prefill_tc_kernel<T, 2> : (poly == 1 ? prefill_tc_kernel<T, 1> : prefill_tc_kernel<T, 0>);
   static thread_local int configured_device = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<T, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: cannot reserve %d bytes of shared memory: %s", fn, kSmemTotal, cudaGetErrorString(e));
     configured_device = dev;
   }
@@ -669,23 +812,11 @@ int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const 
   const long long n_items = static_cast<long long>(n_seqs) * a.n_qtiles_max * q_heads;
   if (n_items > 0x7fffffffll) return fail(PKV_E_UNSUPPORTED, "%s: %lld work items; at most 2^31 - 1 per call", fn, n_items);
   a.n_items = static_cast<int>(n_items);
-  // Ticket counters: one pair per launch in flight, taken round-robin; found once per device.
-  static std::atomic<unsigned> launch_seq{0};
-  static thread_local int counters_device = -1;
-  static thread_local unsigned int* ticket_base = nullptr;
-  static thread_local unsigned int* done_base = nullptr;
-  if (counters_device != dev) {
-    void *t = nullptr, *d = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&t, g_prefill_ticket);
-    if (e == cudaSuccess) e = cudaGetSymbolAddress(&d, g_prefill_done);
-    if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: cudaGetSymbolAddress: %s", fn, cudaGetErrorString(e));
-    ticket_base = static_cast<unsigned int*>(t);
-    done_base = static_cast<unsigned int*>(d);
-    counters_device = dev;
-  }
-  const unsigned slot = launch_seq.fetch_add(1) % kTicketSlots;
-  a.ticket = ticket_base + slot;
-  a.done = done_base + slot;
+  a.dims = d_dims;
+  a.host_err = error_mirror(may_allocate);
+  const TicketPair tp = ticket_pair_for(static_cast<cudaStream_t>(stream), dev);
+  a.ticket = tp.ticket;
+  a.done = tp.done;
   // Persistent blocks: two per SM, or one per item if there are fewer.
   static thread_local int sms = 0;
   if (!sms) {
@@ -695,6 +826,29 @@ int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const 
   const int blocks = static_cast<int>(std::min<long long>(n_items, 2ll * sms));
   launch_pdl(kern, dim3(blocks), dim3(kThreads), kSmemTotal, static_cast<cudaStream_t>(stream), a, qmap, kmap, vmap);
   return check_launch("prefill_tc_kernel");
+}
+
+template int prefill_launch<__nv_bfloat16>(const void*, const void*, const void*, const int*, const int*, const int*,
+                                           const int*, const int*, void*, int, int, int, int, int, int, int, int, float,
+                                           pkv_stream, const int*, bool);
+template int prefill_launch<__half>(const void*, const void*, const void*, const int*, const int*, const int*, const int*,
+                                    const int*, void*, int, int, int, int, int, int, int, int, float, pkv_stream,
+                                    const int*, bool);
+
+namespace {
+
+template <typename T>
+int prefill_impl(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                 const int* table_offset, const int* q_start, const int* q_len, const int* ctx_len, void* out,
+                 int n_tokens, int n_seqs, int max_q_len, int q_heads, int kv_heads, int head_dim, int block_size,
+                 int num_blocks, float scale, pkv_stream stream) {
+  if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return PKV_OK;
+  const int st = check_error_mirror("pkv_prefill_attn");
+  if (st != PKV_OK) return st;
+  if (num_blocks <= 0) return fail(PKV_E_ARG, "pkv_prefill_attn: num_blocks %d must be > 0", num_blocks);
+  return prefill_launch<T>(q, k_cache, v_cache, block_tables, table_offset, q_start, q_len, ctx_len, out, n_tokens,
+                           n_seqs, max_q_len, q_heads, kv_heads, head_dim, block_size, num_blocks, scale, stream,
+                           nullptr, true);
 }
 
 }  // namespace

@@ -82,6 +82,25 @@ def launch_attention_decode(q, k_cache, v_cache, block_tables, table_offset, tok
     _lib.check(fn, st)
 
 
+def mixed_workspace_bytes(n_tokens: int, q_heads: int, kv_heads: int, head_dim: int) -> int:
+    return int(_lib.lib().pkv_mixed_attn_workspace_bytes(n_tokens, q_heads, kv_heads, head_dim))
+
+
+def launch_attention_mixed(q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,
+                           n_tokens: int, q_heads: int, kv_heads: int, head_dim: int, block_size: int,
+                           scale: float, workspace, num_blocks: int = 0, min_run: int = 0, stream=None) -> None:
+    """One call for a step that packs prefill chunks and decode tokens together, the way
+    llm-engine's forward pass calls launch_attention_decode (src/model/cuda/cuda_model.cu:362-377):
+    runs of at least min_run consecutive tokens of one sequence go to the tensor-core prefill kernel,
+    the rest to the decode kernels; the split is made on the device."""
+    fn = f"pkv_mixed_attn_{_suffix(k_cache)}"
+    st = getattr(_lib.lib(), fn)(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(table_offset),
+                                 _ptr(token_seq), _ptr(token_pos), _ptr(out), n_tokens, q_heads, kv_heads, head_dim,
+                                 block_size, num_blocks, C.c_float(scale), min_run, _ptr(workspace),
+                                 workspace.numel() * workspace.element_size(), _stream(stream))
+    _lib.check(fn, st)
+
+
 # llm-engine keeps two names for the same operation, chosen by ENGINE_ATTN
 # (src/model/cuda/cuda_model.cu:554-557); both are one kernel here.
 launch_attention_decode_gqa = launch_attention_decode
@@ -90,9 +109,13 @@ launch_attention_decode_gqa = launch_attention_decode
 class DecodePlan:
     """Split-K work list built once per step and shared by every layer's attention call."""
 
-    def __init__(self, n_tokens: int, q_heads: int, kv_heads: int, head_dim: int, workspace=None, device="cuda"):
+    def __init__(self, n_tokens: int, q_heads: int, kv_heads: int, head_dim: int, workspace=None, device="cuda",
+                 num_blocks: int = 0):
+        """num_blocks: blocks per K/V pool, if known: the kernels' tensor maps then end at the pool
+        (a wrong block id reads zeros); 0 = unknown, as through llm-engine's own launcher signature."""
         import torch
         self.n_tokens, self.q_heads, self.kv_heads, self.head_dim = n_tokens, q_heads, kv_heads, head_dim
+        self.num_blocks = num_blocks
         self.workspace = workspace if workspace is not None else alloc_decode_workspace(
             n_tokens, q_heads, kv_heads, head_dim, device)
         nstage = int(_lib.lib().pkv_decode_plan_staging_bytes(n_tokens, kv_heads))
@@ -111,7 +134,22 @@ class DecodePlan:
                                              self.head_dim, self.staging.data_ptr(), self.staging.numel(), p, n,
                                              _stream(stream), C.byref(self.plan))
         _lib.check("pkv_decode_plan_host", st)
+        self.plan.num_blocks = self.num_blocks
         return self
+
+    def build_host_image(self, token_pos_host) -> int:
+        """The host planner without the upload: the image goes to self.staging (pinned) and its size
+        is returned; the caller copies it to the start of self.workspace, typically as a node of a
+        captured graph that is replayed every step."""
+        import numpy as np
+        pos = np.ascontiguousarray(token_pos_host, dtype=np.int32)
+        n = C.c_size_t(0)
+        st = _lib.lib().pkv_decode_plan_host_image(pos.ctypes.data, self.n_tokens, self.q_heads, self.kv_heads, self.head_dim,
+                                                   self.staging.data_ptr(), self.staging.numel(), self.workspace.numel(),
+                                                   C.byref(self.plan), C.byref(n))
+        _lib.check("pkv_decode_plan_host_image", st)
+        self.plan.num_blocks = self.num_blocks
+        return int(n.value)
 
     def build_host_shared(self, idx, block_size: int, min_saved_bytes: int = -1, stream=None) -> "DecodePlan":
         """Shared-prefix-aware plan from the host copies of the step's index arrays (`idx`: a
@@ -129,6 +167,7 @@ class DecodePlan:
                                                     self.kv_heads, self.head_dim, min_saved_bytes, self.staging.data_ptr(),
                                                     self.staging.numel(), p, n, _stream(stream), C.byref(self.plan))
         _lib.check("pkv_decode_plan_host_shared", st)
+        self.plan.num_blocks = self.num_blocks
         return self
 
     @property
@@ -140,6 +179,7 @@ class DecodePlan:
         st = _lib.lib().pkv_decode_plan_device(_ptr(token_pos), self.n_tokens, self.q_heads, self.kv_heads,
                                                self.head_dim, p, n, _stream(stream), C.byref(self.plan))
         _lib.check("pkv_decode_plan_device", st)
+        self.plan.num_blocks = self.num_blocks
         return self
 
     def attention(self, q, k_cache, v_cache, block_tables, table_offset, token_seq, token_pos, out,

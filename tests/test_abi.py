@@ -23,7 +23,7 @@ def test_every_declared_symbol_is_exported_and_bound(pkv):
     for n in names:
         assert hasattr(L, n), f"{n} declared in pkv.h but not exported by libpkv.so"
         assert n in pkv._lib.SIGNATURES, f"{n} has no ctypes signature"
-    assert L.pkv_abi_version() == 1
+    assert L.pkv_abi_version() == 2
 
 
 def test_reference_launcher_symbols_are_exported(pkv):
@@ -147,3 +147,47 @@ def test_step_pack_errors(pkv):
         pkv.pack_step([t], [-1], 16)
     e = pkv.pack_step([], [], 16)
     assert e.n_tokens == 0 and e.n_seqs == 0
+
+
+def test_recorded_give_up_is_reported_once_by_the_next_attention_call(pkv):
+    """The contract of include/pkv.h, "Bounded waits": the attention call that follows an incomplete
+    launch returns PKV_E_CUDA once and enqueues nothing; the call after that runs normally."""
+    L = pkv.lib()
+    one = 0x1000
+    f = C.c_float(0.125)
+    assert L.pkv_debug_set_reported_flags(2 | 8) == 0
+    st = L.pkv_decode_attn_bf16(one, one, one, one, one, one, one, one, 4, 14, 2, 64, 16, f, None, 0, None)
+    assert st == pkv._lib.PKV_E_CUDA
+    msg = L.pkv_last_error().decode()
+    assert "gave up" in msg and "0xa" in msg
+    # cleared by the report: the same call now gets as far as its argument checks
+    st = L.pkv_decode_attn_bf16(None, one, one, one, one, one, one, one, 4, 14, 2, 64, 16, f, None, 0, None)
+    assert st == pkv._lib.PKV_E_ARG
+    # empty steps never look: they stay silent no-ops
+    assert L.pkv_debug_set_reported_flags(4) == 0
+    assert L.pkv_decode_attn_f16(None, None, None, None, None, None, None, None, 0, 14, 2, 64, 16, f, None, 0, None) == 0
+    plan = pkv._lib.DecodePlan()
+    plan.n_tokens, plan.q_heads, plan.kv_heads, plan.head_dim = 4, 14, 2, 64
+    st = L.pkv_decode_attn_planned_f16(C.byref(plan), one, one, one, one, one, one, one, one, 16, f, one, 1 << 20, None)
+    assert st == pkv._lib.PKV_E_CUDA and "0x4" in L.pkv_last_error().decode()
+    assert L.pkv_debug_set_reported_flags(1) == 0
+    st = L.pkv_prefill_attn_bf16(one, one, one, one, one, one, one, one, one, 4, 1, 4, 14, 2, 64, 16, 8, f, None)
+    assert st == pkv._lib.PKV_E_CUDA
+    st = L.pkv_mixed_attn_bf16(one, one, one, one, one, one, one, one, 0, 14, 2, 64, 16, 0, f, 0, None, 0, None)
+    assert st == 0
+
+
+def test_launcher_symbols_throw_what_the_c_abi_returns(pkv, tmp_path):
+    """engine::launch_attention_decode turns a refusal into std::runtime_error before anything is
+    enqueued, like the reference launchers (src/kernels/attention_decode_gqa.cu:211-224); checked
+    without a GPU on the two refusals that need none."""
+    from tests.shim_util import build_harness
+    H = build_harness(tmp_path)
+    err = C.create_string_buffer(600)
+    one = 0x1000
+    args = lambda n, qh, kvh: (0, 0, one, one, one, one, one, one, one, one, one, one, one, n, qh, kvh, 64, 16, C.c_float(0.125), None, err, 600)
+    assert H.harness_layer(*args(4, 14, 4)) == 1 and b"multiple" in err.value
+    pkv.lib().pkv_debug_set_reported_flags(8)
+    assert H.harness_layer(*args(4, 14, 2)) == 1 and b"gave up" in err.value and b"launch_attention_decode" in err.value
+    assert H.harness_layer(*args(0, 14, 2)) == 0          # an empty step is a silent no-op
+    assert pkv.lib().pkv_mixed_attn_workspace_bytes(300, 14, 2, 64) > pkv.lib().pkv_decode_workspace_bytes(300, 14, 2, 64)

@@ -204,3 +204,26 @@ def test_relocation_invariance_at_full_size(pkv, orc, torch_cuda, workloads):
     v.fill_(0.75)
     out_c = run(kc, vc, idx.block_tables, idx.table_offset, idx.slots)
     assert torch.allclose(out_c.float(), torch.full_like(out_c, 0.75, dtype=torch.float32), rtol=0, atol=0.75 * 2 ** -7)
+
+
+def test_pool_size_in_the_plan_bounds_the_tensor_maps(pkv, orc, torch_cuda):
+    """pkv_decode_plan.num_blocks: with the pool size known the kernels' tensor maps end at the pool.
+    Same step, same bits as with the unbounded maps; and a table entry beyond the pool reads zeros
+    (a finite output) instead of whatever lies behind the pool."""
+    torch = torch_cuda
+    ctx = [700, 15, 3000, 64]
+    case = Case(orc, "bf16", 14, 2, 64, 16, 256, ctx, [1] * len(ctx), seed=21, pkv=pkv)
+    d = case.run_gpu(pkv, torch, "host_plan")
+    want = d["out"].clone()
+    args = (d["q"], d["kc"], d["vc"], d["block_tables"], d["table_offset"], d["token_seq"], d["token_pos"])
+    plan = pkv.DecodePlan(case.N, case.qh, case.kvh, case.hd, num_blocks=case.nb).build_host(case.idx.token_pos)
+    assert plan.plan.num_blocks == case.nb
+    out = torch.zeros_like(want)
+    plan.attention(*args, out, case.bs, case.scale)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    bad = d["block_tables"].clone()
+    bad[3] = case.nb + 5                                    # a block id past the end of the pool
+    plan.attention(d["q"], d["kc"], d["vc"], bad, *args[4:], out, case.bs, case.scale)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all() and pkv.debug_device_flags() == 0

@@ -41,3 +41,17 @@ def test_fused_append_refuses_what_it_cannot_run(pkv, orc, torch_cuda):
     torch_cuda.cuda.synchronize()
     assert torch_cuda.equal(before, d["kc"].view(torch_cuda.int16))
     check_case(case, pkv, torch_cuda, orc, "host_plan")          # the two separate calls do run it
+
+
+def test_configuration_2_at_full_size(pkv, orc, torch_cuda, workloads):
+    """Configuration 2 as BASELINE words it, one layer of it: 64 sequences with contexts uniform in
+    256..2,048 (the workload's own seeded draw), 14 query / 2 kv heads of 64, bf16, block 16, a
+    16,384-block pool dealt in shuffled order.  This is the configuration that takes the append inside
+    the attention launch by default; the two separate calls are checked on the same step."""
+    w = workloads.make("cfg2", layers=1)
+    assert w.n_seqs == 64 and w.ctx.min() >= 256 and w.ctx.max() <= 2048 and w.num_blocks == 16384
+    ctx = [int(c) for c in w.ctx]
+    case = Case(orc, "bf16", w.q_heads, w.kv_heads, w.head_dim, w.block_size, w.num_blocks, ctx, [1] * len(ctx), 1235, pkv)
+    for mode in ("fused_append", "host_plan"):
+        e_ref, e_row = check_case(case, pkv, torch_cuda, orc, mode)
+        assert e_row <= 2e-2
