@@ -345,14 +345,14 @@ int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
 
 template <typename T, int DJ>
 int launch_simt(const DecodeArgs& a, int grid, cudaStream_t stream) {
-  const size_t smem = simt_smem_bytes(a.head_dim);
+  const size_t smem = simt_smem_bytes<T>(a.head_dim);
   auto kern = decode_simt_kernel<T, DJ>;
   if (smem > 48 * 1024) {
     static thread_local int configured_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_device != dev) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
       if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve shared memory: %s", cudaGetErrorString(e));
       configured_device = dev;
     }

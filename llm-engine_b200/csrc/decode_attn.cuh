@@ -226,12 +226,16 @@ __device__ __forceinline__ float4 merge_partials4(const DecodeArgs& a, const Tok
 template <typename T, bool LOG2>
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecodeArgs a) {
   pdl_launch_dependents();
-  pdl_wait();  // the attention kernel's partials
   const int D = a.head_dim;
   const int pairs = a.n_tokens * a.kv_heads;
+  // The split record of this block's first (token, kv head) is part of the plan, which was complete
+  // before the attention kernel started: fetch it while that kernel is still finishing.
+  TokSplit ts_first{0, 0};
+  if (static_cast<int>(blockIdx.x) < pairs) ts_first = a.tok_split[blockIdx.x / a.kv_heads];
+  pdl_wait();  // the attention kernel's partials
   for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
     const int token = pr / a.kv_heads, kvh = pr - token * a.kv_heads;
-    const TokSplit ts = a.tok_split[token];
+    const TokSplit ts = pr == static_cast<int>(blockIdx.x) ? ts_first : a.tok_split[token];
     if (ts.nsplits <= 1 && a.n_peers == 0) continue;
     const int head0 = kvh * a.group;
     if (a.n_peers > 0) {
@@ -558,21 +562,89 @@ __global__ void __launch_bounds__(kDecodeThreads, MIN_BLOCKS) decode_mma_kernel(
 // SIMT path: fp32 K/V (the 1e-5 parity configuration) and every geometry the
 // tensor-core path does not take (head_dim not 64/128, group > 16, block sizes
 // that are not powers of two).  head_dim <= 32 * DJ.
+//
+// Same work decomposition as above (a thread block per (token, key range) x kv head,
+// the tiles of the range dealt to its four warps, the query heads of the group in
+// batches of eight), fp32 arithmetic throughout.  Each warp streams tiles of KT keys
+// through a private two-stage ring in shared memory: the K and V rows of a tile come
+// in with 16-byte cp.async copies (gathered through the block table, rows padded by 16
+// bytes against bank conflicts) while the previous tile is being used.  Scores: lane
+// (h, k) computes q_h . K_k over the whole head dimension from shared memory with
+// 16-byte reads, so a tile costs no shuffles for the dot products; the tile maximum and
+// sum of a head take log2(KT) shuffles.  Output: lane d owns dims d, d + 32, ... of all
+// eight heads and folds the tile's P V in from shared memory.
 // ============================================================================
 constexpr int kSimtHeadBatch = 8;
+
+struct SimtLayout {
+  int kt;            // keys per tile: 8, or 4 for rows beyond 512 bytes
+  int row_bytes;     // one K or V row of one kv head, padded
+  int stage_bytes;   // K tile then V tile
+  int q_ld;          // floats per staged query row
+  size_t off_o, off_m, off_l, off_w, off_p, off_ring, total;
+};
+template <typename T>
+__host__ __device__ inline SimtLayout simt_layout(int D) {
+  SimtLayout L;
+  const int raw = D * static_cast<int>(sizeof(T));
+  L.kt = raw <= 512 ? 8 : 4;
+  L.row_bytes = ((raw + 15) & ~15) + 16;
+  L.stage_bytes = 2 * L.kt * L.row_bytes;
+  L.q_ld = ((D + 3) & ~3) + 4;
+  size_t o = sizeof(float) * kSimtHeadBatch * L.q_ld;                 // sm_q
+  L.off_o = o;  o += sizeof(float) * kDecodeWarps * 16 * (D + 1);      // sm_o
+  L.off_m = o;  o += sizeof(float) * kDecodeWarps * 16;
+  L.off_l = o;  o += sizeof(float) * kDecodeWarps * 16;
+  L.off_w = o;  o += sizeof(float) * (kDecodeWarps + 2) * 16;
+  L.off_p = o;  o += sizeof(float) * kDecodeWarps * (kSimtHeadBatch * 8 + kSimtHeadBatch);   // per warp: p[8][8], alpha[8]
+  o = (o + 15) & ~static_cast<size_t>(15);
+  L.off_ring = o;  o += static_cast<size_t>(kDecodeWarps) * 2 * L.stage_bytes;
+  L.total = o;
+  return L;
+}
+
+template <typename T> __device__ __forceinline__ void load_vec_f32(const unsigned char* p, float (&f)[16 / sizeof(T)]);
+template <> __device__ __forceinline__ void load_vec_f32<float>(const unsigned char* p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load_vec_f32<__half>(const unsigned char* p, float (&f)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 x = __half22float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+}
+template <> __device__ __forceinline__ void load_vec_f32<__nv_bfloat16>(const unsigned char* p, float (&f)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+}
 
 template <typename T, int DJ>
 __global__ void __launch_bounds__(kDecodeThreads) decode_simt_kernel(const DecodeArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int VE = 16 / static_cast<int>(sizeof(T));          // elements per 16-byte piece
   const int D = a.head_dim;
-  const int ldo = D + 1;
-  float* sm_q = reinterpret_cast<float*>(smem_raw);          // [8][D]
-  float* sm_o = sm_q + kSimtHeadBatch * D;                   // [4][16][ldo]
-  float* sm_m = sm_o + kDecodeWarps * 16 * ldo;              // [4][16]
-  float* sm_l = sm_m + kDecodeWarps * 16;
-  float* sm_w = sm_l + kDecodeWarps * 16;                    // [6][16]
+  const SimtLayout L = simt_layout<T>(D);
+  const int KT = L.kt, ldo = D + 1;
+  float* sm_q = reinterpret_cast<float*>(smem_raw);
+  float* sm_o = reinterpret_cast<float*>(smem_raw + L.off_o);
+  float* sm_m = reinterpret_cast<float*>(smem_raw + L.off_m);
+  float* sm_l = reinterpret_cast<float*>(smem_raw + L.off_l);
+  float* sm_w = reinterpret_cast<float*>(smem_raw + L.off_w);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* sm_p = reinterpret_cast<float*>(smem_raw + L.off_p) + warp * (kSimtHeadBatch * 8 + kSimtHeadBatch);   // [h][8]
+  float* sm_alpha = sm_p + kSimtHeadBatch * 8;
+  unsigned char* ring = smem_raw + L.off_ring + static_cast<size_t>(warp) * 2 * L.stage_bytes;
+  const uint32_t ring_u32 = smem_u32(ring);
   const int kv_dim = a.kv_heads * D;
+  const size_t pool_row_bytes = static_cast<size_t>(kv_dim) * sizeof(T);
+  const int row_raw = D * static_cast<int>(sizeof(T));
+  // 16-byte copies need rows that start and end on 16-byte boundaries in the pool
+  const bool vec_ok = (row_raw & 15) == 0 && (pool_row_bytes & 15) == 0 &&
+                      ((reinterpret_cast<uintptr_t>(a.k_cache) | reinterpret_cast<uintptr_t>(a.v_cache)) & 15) == 0;
+  const int pieces = (row_raw + 15) >> 4;                       // 16-byte pieces per row
 
   pdl_launch_dependents();
   pdl_wait();
@@ -584,60 +656,151 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_simt_kernel(const Decod
     int token, kv_begin, kv_len, part;
     load_item(a, item, token, kv_begin, kv_len, part);
     const int* tbl = a.block_tables + __ldg(a.table_offset + __ldg(a.token_seq + token));
-    const T* kc = static_cast<const T*>(a.k_cache) + kvh * D;
-    const T* vc = static_cast<const T*>(a.v_cache) + kvh * D;
+    const unsigned char* kc = static_cast<const unsigned char*>(a.k_cache) + static_cast<size_t>(kvh) * row_raw;
+    const unsigned char* vc = static_cast<const unsigned char*>(a.v_cache) + static_cast<size_t>(kvh) * row_raw;
+    const int n_tiles = (kv_len + KT - 1) / KT;
+    const int n_my = n_tiles > warp ? (n_tiles - warp + kDecodeWarps - 1) / kDecodeWarps : 0;
+
+    // Brings this warp's i-th tile into ring stage i & 1.  Rows past the end of the range are zero-filled.
+    auto stage_tile = [&](int i) {
+      const int t = warp + i * kDecodeWarps;
+      unsigned char* st = ring + (i & 1) * L.stage_bytes;
+      const uint32_t st_u32 = ring_u32 + (i & 1) * L.stage_bytes;
+      for (int c = lane; c < KT * pieces; c += 32) {
+        const int row = c / pieces, piece = c - row * pieces;
+        const int rel = t * KT + row;
+        const bool valid = rel < kv_len;
+        size_t off = 0;
+        if (valid) off = static_cast<size_t>(slot_of(tbl, kv_begin + rel, a.block_size, a.bs_log2)) * pool_row_bytes + piece * 16;
+        const int dst = row * L.row_bytes + piece * 16;
+        if (vec_ok) {
+          cp_async16(st_u32 + dst, kc + off, valid ? 16 : 0);
+          cp_async16(st_u32 + KT * L.row_bytes + dst, vc + off, valid ? 16 : 0);
+        } else {
+          // rows that are not 16-byte granular: element by element
+          const int e0 = piece * VE;
+          for (int e = 0; e < VE; ++e) {
+            T kx = T(0), vx = T(0);
+            if (valid && e0 + e < D) {
+              kx = reinterpret_cast<const T*>(kc + static_cast<size_t>(slot_of(tbl, kv_begin + rel, a.block_size, a.bs_log2)) * pool_row_bytes)[e0 + e];
+              vx = reinterpret_cast<const T*>(vc + static_cast<size_t>(slot_of(tbl, kv_begin + rel, a.block_size, a.bs_log2)) * pool_row_bytes)[e0 + e];
+            }
+            reinterpret_cast<T*>(st + dst)[e] = kx;
+            reinterpret_cast<T*>(st + KT * L.row_bytes + dst)[e] = vx;
+          }
+        }
+      }
+    };
 
     for (int hb = 0; hb < a.group; hb += kSimtHeadBatch) {
       const int rows = min(kSimtHeadBatch, a.group - hb);
       const int head0 = kvh * a.group + hb;
       const T* qb = static_cast<const T*>(a.q) + (static_cast<size_t>(token) * a.q_heads + head0) * D;
-      for (int i = threadIdx.x; i < rows * D; i += kDecodeThreads) sm_q[i] = Elem<T>::to_f32(qb[i]);
+      for (int i = threadIdx.x; i < kSimtHeadBatch * L.q_ld; i += kDecodeThreads) {
+        const int h = i / L.q_ld, d = i - h * L.q_ld;
+        sm_q[i] = (h < rows && d < D) ? Elem<T>::to_f32(qb[static_cast<size_t>(h) * D + d]) : 0.f;
+      }
       __syncthreads();
 
-      float m[kSimtHeadBatch], l[kSimtHeadBatch], acc[kSimtHeadBatch][DJ];
+      // this lane's (head, key) pairs of a tile: pair index lane and lane + 32, key = index % KT
+      const int np = rows * KT;
+      float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+      float acc[kSimtHeadBatch][DJ];
 #pragma unroll
-      for (int h = 0; h < kSimtHeadBatch; ++h) {
-        m[h] = -INFINITY;
-        l[h] = 0.f;
+      for (int h = 0; h < kSimtHeadBatch; ++h)
 #pragma unroll
         for (int j = 0; j < DJ; ++j) acc[h][j] = 0.f;
-      }
-      for (int rel = warp; rel < kv_len; rel += kDecodeWarps) {
-        const int64_t off = slot_of(tbl, kv_begin + rel, a.block_size, a.bs_log2) * kv_dim;
-        float kr[DJ], vr[DJ];
+
+      if (n_my > 0) stage_tile(0);
+      cp_async_commit();
+      for (int i = 0; i < n_my; ++i) {
+        if (i + 1 < n_my) stage_tile(i + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const unsigned char* kst = ring + (i & 1) * L.stage_bytes;
+        const unsigned char* vst = kst + KT * L.row_bytes;
+        const int t = warp + i * kDecodeWarps;
+        const int valid_keys = min(KT, kv_len - t * KT);
+        // ---- scores and the tile's softmax weights ----
 #pragma unroll
-        for (int j = 0; j < DJ; ++j) {
-          const int d = lane + 32 * j;
-          kr[j] = d < D ? Elem<T>::to_f32(kc[off + d]) : 0.f;
-          vr[j] = d < D ? Elem<T>::to_f32(vc[off + d]) : 0.f;
+        for (int s = 0; s < 2; ++s) {
+          const int idx = lane + 32 * s;
+          const bool active = idx < np;
+          const int k = idx % KT, h = active ? idx / KT : 0;
+          float dot = 0.f;
+          if (active) {
+            const unsigned char* krow = kst + k * L.row_bytes;
+            const float* qrow = sm_q + h * L.q_ld;
+            for (int p = 0; p < pieces; ++p) {
+              float kf[VE];
+              load_vec_f32<T>(krow + p * 16, kf);
+#pragma unroll
+              for (int e = 0; e < VE; e += 4) {
+                const float4 qv = *reinterpret_cast<const float4*>(qrow + p * VE + e);
+                dot = fmaf(kf[e], qv.x, dot);
+                dot = fmaf(kf[e + 1], qv.y, dot);
+                dot = fmaf(kf[e + 2], qv.z, dot);
+                dot = fmaf(kf[e + 3], qv.w, dot);
+              }
+            }
+          }
+          const float sc = (active && k < valid_keys) ? dot * a.scale : -INFINITY;
+          float mx = sc;
+          for (int o = 1; o < KT; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          const float mn = fmaxf(m_run[s], mx);                       // finite for every active pair: key 0 of a tile is valid
+          const float al = active ? expf(m_run[s] - mn) : 1.f;        // exp(-inf) = 0 on the first tile
+          const float pw = active ? expf(sc - mn) : 0.f;
+          float ps = pw;
+          for (int o = 1; o < KT; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+          l_run[s] = l_run[s] * al + ps;
+          m_run[s] = mn;
+          if (active) {
+            sm_p[h * 8 + k] = pw;
+            if (k == 0) sm_alpha[h] = al;
+          }
         }
+        __syncwarp();
+        // ---- O = O * alpha + P V, dims lane, lane + 32, ... of every head ----
+        float vv[8][DJ];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+#pragma unroll
+          for (int j = 0; j < DJ; ++j) {
+            const int d = lane + 32 * j;
+            vv[k][j] = (k < KT && d < D) ? Elem<T>::to_f32(reinterpret_cast<const T*>(vst + k * L.row_bytes)[d]) : 0.f;
+          }
 #pragma unroll
         for (int h = 0; h < kSimtHeadBatch; ++h) {
           if (h < rows) {
-            float p = 0.f;
+            const float al = sm_alpha[h];
+            const float4 p0 = *reinterpret_cast<const float4*>(sm_p + h * 8);
+            const float4 p1 = *reinterpret_cast<const float4*>(sm_p + h * 8 + 4);
+            const float pk[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
             for (int j = 0; j < DJ; ++j) {
-              const int d = lane + 32 * j;
-              if (d < D) p += sm_q[h * D + d] * kr[j];
-            }
-            const float s = warp_sum(p) * a.scale;
-            const float mn = fmaxf(m[h], s);
-            const float al = expf(m[h] - mn);  // exp(-inf) = 0 on the first key
-            const float w = expf(s - mn);
-            l[h] = l[h] * al + w;
+              float o = acc[h][j] * al;
 #pragma unroll
-            for (int j = 0; j < DJ; ++j) acc[h][j] = acc[h][j] * al + w * vr[j];
-            m[h] = mn;
+              for (int k = 0; k < 8; ++k) o = fmaf(k < KT ? pk[k] : 0.f, vv[k][j], o);
+              acc[h][j] = o;
+            }
           }
+        }
+        __syncwarp();   // sm_p, sm_alpha and the stage are free for the next tile
+      }
+      cp_async_wait_all();
+      // ---- this warp's partial state for the block-wide merge ----
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const int idx = lane + 32 * s;
+        if (idx < np && idx % KT == 0) {
+          sm_m[warp * 16 + idx / KT] = m_run[s];
+          sm_l[warp * 16 + idx / KT] = l_run[s];
         }
       }
 #pragma unroll
       for (int h = 0; h < kSimtHeadBatch; ++h) {
         if (h < rows) {
-          if (lane == 0) {
-            sm_m[warp * 16 + h] = m[h];
-            sm_l[warp * 16 + h] = l[h];
-          }
 #pragma unroll
           for (int j = 0; j < DJ; ++j) {
             const int d = lane + 32 * j;
@@ -651,9 +814,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_simt_kernel(const Decod
   }
 }
 
-inline size_t simt_smem_bytes(int head_dim) {
-  return sizeof(float) * (static_cast<size_t>(kSimtHeadBatch) * head_dim + kDecodeWarps * 16 * (head_dim + 1) +
-                          2 * kDecodeWarps * 16 + (kDecodeWarps + 2) * 16);
-}
+template <typename T>
+inline size_t simt_smem_bytes(int head_dim) { return simt_layout<T>(head_dim).total; }
 
 }  // namespace pkv

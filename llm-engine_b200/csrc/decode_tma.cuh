@@ -92,11 +92,20 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   }
   __syncwarp();
 
-  // Everything above touched only this block's shared memory.  From here on the
-  // kernel reads what earlier launches on the stream wrote (appended pool rows, the
-  // plan, the workspace the previous merge has finished with).
+  // Everything above touched only this block's shared memory.  What follows reads the plan and the
+  // step's index arrays, which are complete before the predecessor on the stream even starts (they
+  // are built once per step, ahead of every layer's launches, by copies or by kernels that do not
+  // release their dependents early), so the look-ups that lead to a unit's first load -- item, sequence,
+  // table offset, table entries -- run while the predecessor is still finishing.  What the predecessor
+  // itself may have written (pool rows appended by the preceding launch, q and the new k / v rows, the
+  // workspace the previous merge has finished with) is touched only after griddepcontrol.wait, which
+  // every lane executes in issue_next() right before the warp's first load is issued.
   pdl_launch_dependents();
-  pdl_wait();
+  if (lane == 0) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&kmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&vmap) : "memory");
+  }
+  bool waited = false;
   const int n_items = TOK > 1 ? a.n_shared : (a.direct ? a.n_tokens : a.header->n_items);
   const int total = n_items * a.kv_heads;
   const int gw = blockIdx.x * WARPS + warp, GW = gridDim.x * WARPS;
@@ -145,6 +154,10 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     int ent[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) ent[m] = __shfl_sync(0xffffffffu, i_ent, box0 + m - i_ent_base);
+    if (!waited) {
+      pdl_wait();
+      waited = true;
+    }
     // The slot's previous contents were read with ordinary loads (ldmatrix) by all
     // lanes; order those before the asynchronous-proxy write that refills it.
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");

@@ -78,10 +78,11 @@ constexpr int kQBytes = kQTile * 128;            // 128 rows x 128 bytes
 constexpr int kKBytes = kKTile * 128;            // one K (or V, or P) tile: 64 keys x 128 bytes / 128 rows x 64 keys
 constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kSmemQ + 2 * kQBytes;                // two Q tiles (this item's and the next), then kKVStages x (K, V)
-constexpr int kSmemTotal = kSmemKV + kKVStages * 2 * kKBytes + 1024;   // 97 KB: two blocks per SM
-constexpr int kThreads = 192, kProducerWarp = 4, kMmaWarp = 5;
+constexpr int kSmemOnes = kSmemKV + kKVStages * 2 * kKBytes; // a V-shaped tile of 1.0: P x ones = row sums
+constexpr int kSmemTotal = kSmemOnes + kKBytes + 1024;       // 105 KB: two blocks per SM
+constexpr int kThreads = 192, kProducerWarp = 4, kMmaWarp = 5;   // warps 0-3: softmax, one thread per row of the tile
 constexpr uint32_t kTmemCols = 256;                          // two blocks per SM share the 512 columns
-constexpr uint32_t kTmemS = 0, kTmemP = 128, kTmemO = 192;   // S0 @0, S1 @64 (fp32 scores), P0 @128, P1 @160 (16-bit pairs), O @192 (64)
+constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemL = 192;   // S0 @0, S1 @64, O @128 (64) with the row sums right behind (16)
 constexpr int kMaxRanked = 256;       // launches of up to this many (sequence, tile) groups hand them out longest first
 constexpr float kRescaleThreshold = 8.f;                     // in log2 units: P stays below 2^8
 
@@ -134,13 +135,6 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -200,40 +194,6 @@ __device__ __forceinline__ void ffma2(float a0, float a1, float s, float n, floa
       : "f"(a0), "f"(a1), "f"(s), "f"(n));
 }
 
-// Packed add: (a0, a1) += (b0, b1) in one instruction.
-__device__ __forceinline__ void fadd2(float& a0, float& a1, float b0, float b1) {
-  asm("{\n .reg .b64 ra, rb;\n mov.b64 ra, {%0, %1};\n mov.b64 rb, {%2, %3};\n add.rn.f32x2 ra, ra, rb;\n mov.b64 {%0, %1}, ra;\n}\n"
-      : "+f"(a0), "+f"(a1)
-      : "f"(b0), "f"(b1));
-}
-
-// Packed fused multiply-add with vector operands: (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1).
-__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
-  asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
-      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}\n"
-      : "=f"(d0), "=f"(d1)
-      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
-}
-
-// 2^x for a pair, on the FMA and integer pipes instead of the exponential unit: n = round(x) by the
-// magic-number addition, f = x - n in [-0.5, 0.5], 2^f by a cubic (relative error 7.5e-5, well inside
-// what a 16-bit P keeps), then n added into the exponent field.  x is clamped at -126 first, which
-// also turns the -inf of a masked score into a denormal-sized weight (2^-126) instead of garbage.
-__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& e0, float& e1) {
-  constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  float t0, t1, n0, n1, f0, f1, p0, p1;
-  fma2(t0, t1, x0, x1, 1.f, 1.f, kMagic, kMagic);
-  fma2(n0, n1, t0, t1, 1.f, 1.f, -kMagic, -kMagic);
-  fma2(f0, f1, n0, n1, -1.f, -1.f, x0, x1);
-  fma2(p0, p1, f0, f1, 0.0551716685f, 0.0551716685f, 0.2426111251f, 0.2426111251f);
-  fma2(p0, p1, p0, p1, f0, f1, 0.6932609677f, 0.6932609677f);
-  fma2(p0, p1, p0, p1, f0, f1, 0.9999280572f, 0.9999280572f);
-  e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-}
-
 // Three-input maximum: one instruction on this architecture.
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -257,36 +217,33 @@ struct ItemDesc {
   int pad[2];
 };
 
-// POLY: of every four pairs of scores, how many take their exponentials from ex2_poly2 instead of
-// the exponential unit (0, 1 or 2).
-template <typename T, int POLY>
+template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
     prefill_tc_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap qmap,
                       const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr uint32_t kIdescQK = instr_desc(kBf16, kKTile, false);
-  constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd, true);
+  constexpr uint32_t kIdescPV = instr_desc(kBf16, kHd + 16, true);   // 64 output dims + 16 row-sum columns
   constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[4 + 2 * kKVStages + 8];
+  __shared__ __align__(8) unsigned long long bars[4 + 2 * kKVStages + 6];
   __shared__ __align__(16) ItemDesc s_item[2];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV;
+  const uint32_t sQ = base + kSmemQ, sKV = base + kSmemKV, sOnes = base + kSmemOnes;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = KV_FULL + kKVStages, S_FULL = KV_EMPTY + kKVStages,
-         S_READ = S_FULL + 2, P_FULL = S_READ + 2, PV_DONE = P_FULL + 2 };
+  enum { Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = KV_FULL + kKVStages, S_FULL = KV_EMPTY + kKVStages, P_FULL = S_FULL + 2, PV_DONE = P_FULL + 2 };
 
   // ---- on-chip set-up: touches no global memory, so it may overlap the previous launch ----
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(BAR(Q_FULL + i), 1);
-      mbar_init(BAR(Q_EMPTY + i), 1 + 128);   // tcgen05.commit after the item's last Q K^T, and every softmax thread once it is done with the item
+      mbar_init(BAR(Q_EMPTY + i), 1 + 128);   // tcgen05.commit after the item's last Q K^T, and the softmax threads (one arrival of 32 per warp) once done with the item
     }
     for (int i = 0; i < kKVStages; ++i) {
       mbar_init(BAR(KV_FULL + i), 1);
@@ -294,11 +251,18 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(BAR(S_FULL + i), 1);     // tcgen05.commit after Q K_j^T
-      mbar_init(BAR(S_READ + i), 128);   // every softmax thread, once its row of S_j is in registers
-      mbar_init(BAR(P_FULL + i), 128);   // every softmax thread, after writing its row of P_j
-      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated, P_j consumed
+      mbar_init(BAR(P_FULL + i), 128);   // the softmax threads (one arrival of 32 per warp), after writing their rows of P_j
+      mbar_init(BAR(PV_DONE + i), 1);    // tcgen05.commit after P_j V_j: O updated
     }
     mbar_fence_init();
+  }
+  if (threadIdx.x < kKTile) {
+    // the tile of ones that makes columns 64..79 of every P V product the row sums of P
+    const uint32_t one2 = pack2<T>(1.f, 1.f);
+    unsigned char* orow = base_ptr + kSmemOnes + threadIdx.x * 128;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(orow + ch * 16) = make_uint4(one2, one2, one2, one2);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
@@ -455,32 +419,27 @@ __global__ void __launch_bounds__(kThreads, 2)
     // tensor pipe retires them (48 cycles for 128 x 64 x 16 from shared memory, 45 with A in tensor
     // memory), a blocking try_wait costs a few hundred cycles even on a completed phase (mbar_wait
     // looks first), and the scalar code of a lone thread runs at one dependent instruction every
-    // few cycles, so the schedule is kept to three waits, eight MMAs and three commits per key tile.
-    // Scores run TWO tiles ahead of the softmax warps: S_{g+2} goes into the buffer of S_g as soon
-    // as every softmax thread has S_g in registers (S_READ), which is early in its work on tile g,
-    // because P has buffers of its own and does not overwrite the scores it came from.  While the
-    // softmax warps work on tile g, S_{g+1} is complete and S_{g+2} is in the pipe, so they never
-    // wait for scores in steady state, and the pipe's queue (shared with the SM's other block) is
-    // off their critical path.  Then O += P_g V_g once P_g is there (A operand from tensor memory,
-    // B the V tile as MN-major operand).
+    // few cycles, so the schedule is kept to two waits, eight MMAs and three commits per key tile:
+    //  * no separate "S buffer free" barrier: a softmax thread has read S_{g-1} and written P_{g-1}
+    //    over it before it arrives on P_FULL_{g-1}; this thread waits for that, issues P_{g-1} V_{g-1},
+    //    and only then S_{g+1} into the same buffer (instructions of one thread execute in order);
+    //  * O += P V and the row sums of P come out of ONE MMA of N = 80: the B operand is MN-major,
+    //    its first 64 columns are the V tile and its next column block, one leading-dimension
+    //    offset away, is a tile of ones.
     // It does not wait for the softmax warps' epilogue: after an item's last P V it goes on to the
     // next item's first scores.
     if (lane == 0) {
       const uint64_t desc_q0 = smem_desc(sQ), desc_k0 = smem_desc(sKV);
-      int n = 0, g = 0;       // g: key tiles whose P V has been issued (all items)
-      int gq = 0;             // key tiles whose Q K^T has been issued
+      int n = 0, g = 0;
       while (!dead) {
         const int qb = n & 1;
         WAIT(BAR(Q_FULL + qb), (n >> 1) & 1);
         const int n_kt = s_item[qb].n_kt;
         if (n_kt <= 0 || dead) break;
         const uint64_t desc_q = desc_q0 + ((qb * kQBytes) >> 4);
-        const int g_end = g + n_kt;          // first tile of the next item
-        auto issue_qk = [&]() {
-          // scores of tile gq into buffer gq & 1, whose previous tenant (tile gq - 2) must have been read
-          const int st = gq % kKVStages, sb = gq & 1;
-          if (gq >= 2) WAIT(BAR(S_READ + sb), ((gq - 2) >> 1) & 1);
-          WAIT(BAR(KV_FULL + st), (gq / kKVStages) & 1);
+        auto issue_qk = [&](int gg, bool last_of_item) {
+          const int st = gg % kKVStages, sb = gg & 1;
+          WAIT(BAR(KV_FULL + st), (gg / kKVStages) & 1);
           tc_fence_after();
           // descriptors differ only in their 14-bit start-address field: add to the low word
           const uint64_t kd = desc_k0 + ((st * 2 * kKBytes) >> 4);
@@ -488,18 +447,17 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int ks = 0; ks < kHd / 16; ++ks)
             tc_mma(tmem + kTmemS + sb * 64, desc_q + 2 * ks, kd + 2 * ks, kIdescQK, ks > 0);
           tc_commit(BAR(S_FULL + sb));
-          ++gq;
-          if (gq == g_end) tc_commit(BAR(Q_EMPTY + qb));      // the Q tile has been read for the last time
+          if (last_of_item) tc_commit(BAR(Q_EMPTY + qb));      // the Q tile has been read for the last time
         };
-        issue_qk();
-        if (gq < g_end) issue_qk();
+        issue_qk(g, n_kt == 1);
         for (int j = 0; j < n_kt; ++j, ++g) {
           const int st = g % kKVStages, sb = g & 1;
-          if (gq < g_end) issue_qk();                            // tile g + 2 (waits for S_g to have been read)
+          if (j + 1 < n_kt) issue_qk(g + 1, j + 2 == n_kt);
           WAIT(BAR(P_FULL + sb), (g >> 1) & 1);
           tc_fence_after();
-          const uint64_t vd = smem_desc(sKV + st * 2 * kKBytes + kKBytes);
-          const uint32_t p_addr = tmem + kTmemP + sb * 32;
+          const uint32_t v_base = sKV + st * 2 * kKBytes + kKBytes;
+          const uint64_t vd = smem_desc(v_base, sOnes - v_base);
+          const uint32_t p_addr = tmem + kTmemS + sb * 64;      // P lies over the first 32 columns of its S buffer
 #pragma unroll
           for (int kk = 0; kk < kKTile / 16; ++kk)
             tc_mma_ts(tmem + kTmemO, p_addr + kk * 8, vd + kk * (kBox >> 4), kIdescPV, (j | kk) != 0);
@@ -523,11 +481,10 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (d.n_kt <= 0 || dead) break;
       const int n_kt = d.n_kt, kv_total = d.kv_total, rows_here = d.rows_here;
       const int limit = d.limit0 + min(r, rows_here - 1);   // last visible key position of this row
-      // Reference maximum of the row.  It follows the true running maximum lazily: O stays in tensor
-      // memory and is only rescaled (with the row sum, which lives in this thread) when the maximum
-      // has grown by more than 2^8, so most tiles cost no read-modify-write of the accumulator.
+      // Reference maximum of the row.  It follows the true running maximum lazily: O and the row
+      // sum stay in tensor memory and are only rescaled when the maximum has grown by more than
+      // 2^8, so most tiles cost no read-modify-write of the accumulator at all.
       float m_used = -INFINITY;
-      float l_acc[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // row sum of P, four chains of packed pairs
 
       for (int j = 0; j < n_kt; ++j, ++g) {
         const int sb = g & 1;
@@ -546,9 +503,6 @@ __global__ void __launch_bounds__(kThreads, 2)
             sc[32 + i] = __uint_as_float(v1[i]);
           }
         }
-        // the scores are in registers: their buffer may take the scores of the tile after next
-        tc_fence_before();
-        mbar_arrive(BAR(S_READ + sb));
         // Causal mask, only on tiles that reach past some row's last visible key (warp-uniform test).
         if (__any_sync(0xffffffffu, k0 + kKTile - 1 > limit)) {
 #pragma unroll
@@ -567,8 +521,8 @@ __global__ void __launch_bounds__(kThreads, 2)
         if (j == 0) {
           m_used = mx;                                 // finite: key 0 is visible to every row
         } else if (__any_sync(0xffffffffu, (mx - m_used) * sl2 > kRescaleThreshold)) {
-          // Rare: bring this warp's rows of O and their row sums to the new maximum.  Each thread owns
-          // its own tensor-memory lane; the previous tile's P V must have landed and this tile's
+          // Rare: bring this warp's rows of O and of the row sums to the new maximum.  Each thread
+          // owns its own tensor-memory lane; the previous tile's P V must have landed and this tile's
           // cannot start before this thread has arrived on P_FULL below.
           WAIT(BAR(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1);
           tc_fence_after();
@@ -576,9 +530,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           const float f = ex2_approx((m_used - m_new) * sl2);
           m_used = m_new;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) { l_acc[c][0] *= f; l_acc[c][1] *= f; }
-#pragma unroll
-          for (int blk = 0; blk < kHd / 32; ++blk) {
+          for (int blk = 0; blk < 3; ++blk) {          // O: columns 128..191, row sums: 192..223
             uint32_t v[32];
             tc_ld32(tmem + lane_addr + kTmemO + blk * 32, v);
             tc_wait_ld();
@@ -588,9 +540,9 @@ __global__ void __launch_bounds__(kThreads, 2)
           }
         }
         const float neg = -m_used * sl2;
-        // P_g goes to its own buffer in tensor memory as packed 16-bit pairs (32 columns), which the
-        // P V of tile g - 2 must have finished reading; that was issued two tiles ago.
-        if (g >= 2) WAIT(BAR(PV_DONE + sb), ((g - 2) >> 1) & 1);
+        // P goes back into tensor memory as packed 16-bit pairs over the first 32 columns of the S
+        // buffer it came from: this thread has all of its own row in registers, and the MMA thread
+        // overwrites the buffer with the scores after next only after it has issued this P V.
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
@@ -598,17 +550,9 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
             ffma2(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1], sl2, neg, x0, x1);
-            float e0, e1;
-            if ((i & 3) < POLY) {
-              ex2_poly2(x0, x1, e0, e1);
-            } else {
-              e0 = ex2_approx(x0);
-              e1 = ex2_approx(x1);
-            }
-            fadd2(l_acc[i & 3][0], l_acc[i & 3][1], e0, e1);
-            pk[i] = pack2<T>(e0, e1);
+            pk[i] = pack2<T>(ex2_approx(x0), ex2_approx(x1));
           }
-          tc_st16(tmem + lane_addr + kTmemP + sb * 32 + c * 16, pk);
+          tc_st16(tmem + lane_addr + kTmemS + sb * 64 + c * 16, pk);
         }
         if (j == n_kt - 1 && kv_total - k0 < kKTile) {
           // Keys past the end of the sequence in the last tile: their P is zero, but the V rows
@@ -624,16 +568,18 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(BAR(P_FULL + sb));
+        __syncwarp();
+        if (lane == 0) mbar_arrive_warp(BAR(P_FULL + sb));
       }
       // epilogue: O / row sum.  The next item's first P V cannot overwrite O before this thread has
       // arrived on that tile's P_FULL, which it does after the loads below.
       WAIT(BAR(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1);
       tc_fence_after();
       {
-        uint32_t o0[32], o1[32];
+        uint32_t o0[32], o1[32], lv[32];
         tc_ld32(tmem + lane_addr + kTmemO, o0);
         tc_ld32(tmem + lane_addr + kTmemO + 32, o1);
+        tc_ld32(tmem + lane_addr + kTmemL, lv);
         tc_wait_ld();
         tc_fence_before();
         // The row goes through shared memory so that the global stores are whole 128-byte lines
@@ -641,8 +587,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         // area is the item's own Q tile, which nothing reads any more (the item's last Q K^T has
         // completed); each warp stages and drains its own 32 rows, 16-byte pieces XOR-swizzled
         // against bank conflicts.
-        const float l = (l_acc[0][0] + l_acc[0][1]) + (l_acc[1][0] + l_acc[1][1]) + ((l_acc[2][0] + l_acc[2][1]) + (l_acc[3][0] + l_acc[3][1]));
-        const float inv = 1.f / l;
+        const float inv = 1.f / __uint_as_float(lv[0]);
         unsigned char* stage = base_ptr + kSmemQ + qb * kQBytes;
         unsigned char* my_row = stage + r * 128;
 #pragma unroll
@@ -672,7 +617,8 @@ __global__ void __launch_bounds__(kThreads, 2)
       // The Q buffer may be refilled (by TMA) once every thread is done with it: the item's
       // description, and the staging of its output.
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      mbar_arrive(BAR(Q_EMPTY + qb));
+      __syncwarp();
+      if (lane == 0) mbar_arrive_warp(BAR(Q_EMPTY + qb));
       ++n;
     }
   }
@@ -787,16 +733,12 @@ int prefill_launch(const void* q, const void* k_cache, const void* v_cache, cons
   st = make_pool_tensor_map(&qmap, q, is_bf16, q_heads * head_dim, kQTile, static_cast<uint64_t>(n_tokens));
   if (st != PKV_OK) return st;
 
-  // PKV_PREFILL_POLY = 0 | 1 | 2: share (in quarters) of the exponentials computed on the FMA pipe.
-  static const int poly = [] { const char* e = std::getenv("PKV_PREFILL_POLY"); return (e && *e >= '0' && *e <= '2') ? *e - '0' : 0; }();
-  auto kern = poly == 2 ? prefill_tc_kernel<T, 2> : (poly == 1 ? prefill_tc_kernel<T, 1> : prefill_tc_kernel<T, 0>);
+  auto kern = prefill_tc_kernel<T>;
   static thread_local int configured_device = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<T, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return fail(PKV_E_CUDA, "%s: cannot reserve %d bytes of shared memory: %s", fn, kSmemTotal, cudaGetErrorString(e));
     configured_device = dev;
   }

@@ -63,6 +63,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
+// One lane arrives for its whole warp (count 32): call after __syncwarp().  Thirty-two lanes arriving
+// on one barrier word one by one serialise in the shared-memory pipe and delay the warp's next
+// shared-memory operation by a couple of hundred cycles.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], 32;\n" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
