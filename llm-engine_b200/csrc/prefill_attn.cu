@@ -765,7 +765,9 @@ int prefill_launch(const void* q, const void* k_cache, const void* v_cache, cons
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
   }
-  const int blocks = static_cast<int>(std::min<long long>(n_items, 2ll * sms));
+  // PKV_PREFILL_BLOCKS_PER_SM = 1: half the persistent grid (a measurement aid: what one block per SM does alone)
+  static const int per_sm = [] { const char* e = std::getenv("PKV_PREFILL_BLOCKS_PER_SM"); return (e && e[0] == '1') ? 1 : 2; }();
+  const int blocks = static_cast<int>(std::min<long long>(n_items, static_cast<long long>(per_sm) * sms));
   launch_pdl(kern, dim3(blocks), dim3(kThreads), kSmemTotal, static_cast<cudaStream_t>(stream), a, qmap, kmap, vmap);
   return check_launch("prefill_tc_kernel");
 }
