@@ -83,3 +83,39 @@ def test_a_sequence_that_appears_in_two_runs(pkv, orc, torch_cuda):
     case.k_bits, case.k = cast_like_reference(orc, f(case.N, 2 * 64), "bf16")
     case.v_bits, case.v = cast_like_reference(orc, f(case.N, 2 * 64), "bf16")
     run_mixed(case, pkv, torch_cuda, orc)
+
+
+def test_configuration_4_through_the_mixed_entry_point_equals_the_prefill_call(pkv, orc, torch_cuda, workloads):
+    """Configuration 4 at full size (32 sequences, 512-token chunks over 0..1,536 cached tokens, 16,384 packed
+    rows) handed over the way llm-engine hands a step over: token_seq / token_pos only.  The router must find the
+    32 chunks and give the prefill kernel the records a caller of pkv_prefill_attn_* would have passed, so the two
+    outputs agree bit for bit; a sample of rows is checked against the CPU checker."""
+    torch = torch_cuda
+    w = workloads.make("cfg4", layers=1)
+    bs, kv_dim, H = w.block_size, w.kv_dim, w.q_heads * w.head_dim
+    tabs, pos, _ = w.step_tokens()
+    idx = pkv.pack_step(tabs, pos, bs)
+    N = idx.n_tokens
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda *s: torch.randn(s, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    kc, vc, q = rnd(w.num_blocks * bs, kv_dim), rnd(w.num_blocks * bs, kv_dim), rnd(N, H)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).cuda()
+    d_tab, d_off, d_seq, d_pos = i32(idx.block_tables), i32(idx.table_offset), i32(idx.token_seq), i32(idx.token_pos)
+    q_len = w.new.astype(np.int32)
+    q_start = np.concatenate([[0], np.cumsum(q_len)[:-1]]).astype(np.int32)
+    direct = torch.zeros((N, H), dtype=torch.bfloat16, device="cuda")
+    pkv.launch_attention_prefill(q, kc, vc, d_tab, d_off, i32(q_start), i32(q_len), i32(w.ctx.astype(np.int32)), direct, N,
+                                 w.n_seqs, int(q_len.max()), w.q_heads, w.kv_heads, w.head_dim, bs, w.num_blocks, w.scale)
+    routed = torch.zeros_like(direct)
+    ws = torch.empty(pkv.mixed_workspace_bytes(N, w.q_heads, w.kv_heads, w.head_dim), dtype=torch.uint8, device="cuda")
+    pkv.launch_attention_mixed(q, kc, vc, d_tab, d_off, d_seq, d_pos, routed, N, w.q_heads, w.kv_heads, w.head_dim, bs,
+                               w.scale, ws, num_blocks=w.num_blocks)
+    torch.cuda.synchronize()
+    assert pkv.debug_device_flags() == 0
+    assert torch.equal(direct.view(torch.int16), routed.view(torch.int16))
+    sample = np.unique(np.concatenate([np.arange(0, N, 997), [0, 511, 512, N - 1]]))
+    bits = lambda t: orc.from_bf16_bits(t.view(torch.int16).cpu().numpy().view(np.uint16))
+    want = orc.paged_attention(bits(q)[sample], bits(kc), bits(vc), idx.block_tables, idx.table_offset, idx.token_seq[sample],
+                               idx.token_pos[sample], w.q_heads, w.kv_heads, w.head_dim, bs, w.scale, threads=8)
+    e_ref, e_row = rel_errors(bits(routed)[sample].reshape(-1, 64), want.reshape(-1, 64))
+    assert e_ref <= TOL["bf16"] and e_row <= TOL["bf16"], (e_ref, e_row)
