@@ -31,7 +31,7 @@ unsigned int* error_mirror(bool create) {
   void* p = nullptr;
   if (cudaHostAlloc(&p, 64, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess && p) {
     std::memset(p, 0, 64);
-    g_mirror = static_cast<unsigned int*>(p);
+    __atomic_store_n(&g_mirror, static_cast<unsigned int*>(p), __ATOMIC_RELEASE);
   } else {
     cudaGetLastError();
   }
@@ -39,6 +39,9 @@ unsigned int* error_mirror(bool create) {
 }
 
 unsigned int take_error_mirror() {
+  // the common case -- nothing recorded -- is two plain loads, no lock and no write
+  unsigned int* m = __atomic_load_n(&g_mirror, __ATOMIC_ACQUIRE);
+  if (__atomic_load_n(&g_plain, __ATOMIC_RELAXED) == 0 && (!m || __atomic_load_n(m, __ATOMIC_RELAXED) == 0)) return 0;
   std::lock_guard<std::mutex> lock(g_mu);
   unsigned int v = g_plain;
   g_plain = 0;
