@@ -50,7 +50,7 @@ WORKLOAD_TEXT = {
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the decode attention kernel, from the
 # ncu captures summarised under profiles/ (same per-launch workload as the default seed of each configuration).
 NCU_TRAFFIC = {
-    "cfg3": {"bytes": 429279488, "source": "profiles/decode_tma_kernel_cfg3_ncu_full.md (421.21 MB read + 8.07 MB written)"},
+    "cfg3": {"bytes": 428955648, "source": "profiles/decode_tma_kernel_cfg3_ncu_full.md (421.21 MB read + 7.75 MB written)"},
 }
 METRIC = "decode tok/s (K/V append + paged decode attention over all layers)"
 
