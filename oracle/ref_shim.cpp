@@ -7,6 +7,9 @@
 //   engine::KVCacheManager / BlockTable    include/engine/kv_cache.h, src/kv_cache/block_allocator.cpp
 //   engine::ThreadPool                     include/engine/parallel.h
 //   engine::f32_to_bf16 & friends          include/engine/tensor.h:20-62
+//   engine::Scheduler                      include/engine/scheduler.h, src/scheduler/scheduler.cpp
+//                                          (only to GENERATE realistic steps: which slices a real
+//                                          engine run puts into a step, with which block tables)
 // so that the plain-C restatement in paged_oracle.c, and through it the CUDA
 // kernels, can be compared with the real thing.  It is built into
 // oracle/_ref/libpkv_ref.so, which is never linked into the shipped library.
@@ -17,6 +20,7 @@
 #include "engine/kv_cache.h"
 #include "engine/ops.h"
 #include "engine/parallel.h"
+#include "engine/scheduler.h"
 #include "engine/tensor.h"
 
 using engine::BlockTable;
@@ -177,6 +181,77 @@ void ref_paged_attention(const float* q, const float* k_cache, const float* v_ca
   };
   engine::ThreadPool pool(threads);
   pool.parallel_for(static_cast<int64_t>(n_tokens) * q_heads, body);
+}
+
+// ---- the reference's scheduler as a generator of steps ------------------------------
+// One KVCacheManager + Scheduler pair (include/engine/scheduler.h:60-75); requests are added with
+// their prompt tokens, every ref_sched_step() is one Scheduler::schedule(), and ref_sched_done()
+// is Scheduler::on_step_done() with the caller's "sampled" tokens.
+struct RefSched {
+  KVCacheManager kv;
+  engine::Scheduler sched;
+  std::vector<engine::SequencePtr> seqs;
+  engine::StepInput step;
+  RefSched(int nb, int bs, bool prefix, engine::SchedulerConfig cfg) : kv(nb, bs, prefix), sched(cfg, kv) {}
+};
+
+void* ref_sched_new(int num_blocks, int block_size, int prefix, int max_num_seqs, int max_batched_tokens, int chunk) {
+  engine::SchedulerConfig cfg;
+  cfg.max_num_seqs = max_num_seqs;
+  cfg.max_num_batched_tokens = max_batched_tokens;
+  cfg.prefill_chunk_size = chunk;
+  try { return new RefSched(num_blocks, block_size, prefix != 0, cfg); } catch (...) { return nullptr; }
+}
+void ref_sched_delete(void* h) { delete static_cast<RefSched*>(h); }
+// returns the sequence's id (its index in arrival order)
+int ref_sched_add(void* h, const int32_t* prompt, int n, int max_tokens) {
+  auto* r = static_cast<RefSched*>(h);
+  auto s = std::make_shared<engine::Sequence>();
+  s->id = r->seqs.size();
+  s->tokens.assign(prompt, prompt + n);
+  s->prompt_len = n;
+  s->params.max_tokens = max_tokens;
+  s->params.ignore_eos = true;
+  r->seqs.push_back(s);
+  r->sched.add(s);
+  return static_cast<int>(s->id);
+}
+// One scheduling round.  Returns the number of slices (prefill slices first, then decode);
+// slice i is (seq_id[i], start[i], len[i], needs_logits[i]).
+int ref_sched_step(void* h, int* seq_id, int* start, int* len, int* needs_logits, int cap) {
+  auto* r = static_cast<RefSched*>(h);
+  r->step = r->sched.schedule();
+  const int n = static_cast<int>(r->step.slices.size());
+  for (int i = 0; i < n && i < cap; i++) {
+    const auto& sl = r->step.slices[i];
+    seq_id[i] = static_cast<int>(sl.seq->id);
+    start[i] = sl.start;
+    len[i] = sl.len;
+    needs_logits[i] = sl.needs_logits ? 1 : 0;
+  }
+  return n;
+}
+int ref_sched_seq_blocks(void* h, int seq, int32_t* out, int cap) {
+  auto* r = static_cast<RefSched*>(h);
+  const auto& b = r->seqs[seq]->block_table.blocks;
+  for (size_t i = 0; i < b.size() && static_cast<int>(i) < cap; i++) out[i] = b[i];
+  return static_cast<int>(b.size());
+}
+int ref_sched_seq_tokens(void* h, int seq, int32_t* out, int cap) {
+  auto* r = static_cast<RefSched*>(h);
+  const auto& t = r->seqs[seq]->tokens;
+  for (size_t i = 0; i < t.size() && static_cast<int>(i) < cap; i++) out[i] = t[i];
+  return static_cast<int>(t.size());
+}
+void ref_sched_done(void* h, const int32_t* sampled, int n) {
+  auto* r = static_cast<RefSched*>(h);
+  r->sched.on_step_done(r->step, std::vector<int32_t>(sampled, sampled + n));
+}
+int ref_sched_has_work(void* h) { return static_cast<RefSched*>(h)->sched.has_work() ? 1 : 0; }
+// out[4]: steps, preemptions, admitted, finished
+void ref_sched_stats(void* h, uint64_t* out) {
+  const auto& s = static_cast<RefSched*>(h)->sched.stats();
+  out[0] = s.steps; out[1] = s.preemptions; out[2] = s.admitted; out[3] = s.finished;
 }
 
 }  // extern "C"

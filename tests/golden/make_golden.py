@@ -8,6 +8,9 @@ Outputs:
     tests/golden/attn_tiny_f32.npz    one TinyLlama-shaped step, mixed decode + chunk tokens
     tests/golden/allocator_trace.json a random KVCacheManager trace with every observable result
     tests/golden/casts.json           bf16 / f16 conversions of edge-case floats
+    tests/golden/engine_trace.npz     the steps the reference's own Scheduler builds for a small serving run
+                                      (chunked prefill, decode, prefix-cache hits, preemption with recompute):
+                                      per step the slices and every slice's block table at that moment
 """
 import json
 import os
@@ -20,6 +23,96 @@ sys.path.insert(0, ROOT)
 import oracle  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def content_keys(tokens):
+    """key[p] identifies the content of positions 0..p (K/V at p depend on all of them in a real model): two
+    sequences with the same first p + 1 tokens -- a shared, cached prefix -- get the same key."""
+    keys = np.empty(len(tokens), dtype=np.uint64)
+    k = 0
+    for p, t in enumerate(tokens):
+        k = (k * 6364136223846793005 + int(t) + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        keys[p] = k
+    return keys
+
+
+def engine_trace(ref, path, seed=5):
+    """Drives engine::Scheduler + engine::KVCacheManager (compiled from the reference's sources) the way
+    Engine::step does -- schedule(), run the step, on_step_done(sampled) -- on a pool small enough to force
+    preemptions, with prompts that share cached prefixes, and records what the attention path is handed."""
+    import ctypes as C
+    L = ref.lib
+    L.ref_sched_new.restype = C.c_void_p
+    L.ref_sched_new.argtypes = [C.c_int] * 6
+    for name, args in (("ref_sched_delete", [C.c_void_p]), ("ref_sched_add", [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+                       ("ref_sched_step", [C.c_void_p] * 5 + [C.c_int]), ("ref_sched_seq_blocks", [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
+                       ("ref_sched_seq_tokens", [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
+                       ("ref_sched_done", [C.c_void_p, C.c_void_p, C.c_int]), ("ref_sched_has_work", [C.c_void_p]),
+                       ("ref_sched_stats", [C.c_void_p, C.c_void_p])):
+        getattr(L, name).argtypes = args
+        getattr(L, name).restype = C.c_int
+    rng = np.random.default_rng(seed)
+    bs, num_blocks, max_seqs, budget, chunk = 16, 72, 8, 320, 128
+    h = L.ref_sched_new(num_blocks, bs, 1, max_seqs, budget, chunk)
+    common = rng.integers(0, 30000, size=3 * bs + 5).astype(np.int32)           # a shared system prompt: 3 full blocks + 5
+    prompts = []
+    for i in range(14):
+        n = int(rng.integers(10, 300))
+        own = rng.integers(0, 30000, size=n).astype(np.int32)
+        prompts.append(np.concatenate([common, own]) if i % 3 == 0 else own)
+    arrivals = {0: [0, 1, 2, 3], 2: [4, 5], 5: [6], 9: [7, 8, 9], 15: [10, 11], 22: [12, 13]}   # step -> requests that arrive before it
+    max_new = [int(x) for x in rng.integers(60, 260, size=len(prompts))]
+    ids = {}
+    steps = []
+    cap = 64
+    a_seq, a_start, a_len, a_log = (np.zeros(cap, np.int32) for _ in range(4))
+    step_no = 0
+    while step_no < 320:
+        for r in arrivals.get(step_no, []):
+            ids[r] = L.ref_sched_add(h, prompts[r].ctypes.data, prompts[r].size, max_new[r])
+        if not L.ref_sched_has_work(h) and step_no > max(arrivals):
+            break
+        n = L.ref_sched_step(h, a_seq.ctypes.data, a_start.ctypes.data, a_len.ctypes.data, a_log.ctypes.data, cap)
+        assert n <= cap
+        if n == 0:
+            step_no += 1
+            continue
+        rec = {"seq": a_seq[:n].copy(), "start": a_start[:n].copy(), "len": a_len[:n].copy(), "tables": []}
+        sampled = []
+        for i in range(n):
+            sid = int(a_seq[i])
+            tb = np.zeros(num_blocks, np.int32)
+            nb = L.ref_sched_seq_blocks(h, sid, tb.ctypes.data, num_blocks)
+            rec["tables"].append(tb[:nb].copy())
+            if a_log[i]:
+                sampled.append((sid * 7919 + (int(a_start[i]) + int(a_len[i])) * 104729) % 30000)
+        steps.append(rec)
+        smp = np.asarray(sampled, dtype=np.int32)
+        L.ref_sched_done(h, smp.ctypes.data, smp.size)
+        step_no += 1
+    st = np.zeros(4, np.uint64)
+    L.ref_sched_stats(h, st.ctypes.data)
+    # every sequence's tokens as they stand at the end (prompt + what was "sampled"): tokens are only ever
+    # appended, so the content of positions 0..p at any earlier step is a prefix of this
+    seq_tokens = []
+    for sid in range(len(ids)):
+        tk = np.zeros(4096, np.int32)
+        nt = L.ref_sched_seq_tokens(h, sid, tk.ctypes.data, 4096)
+        seq_tokens.append(tk[:nt].copy())
+    L.ref_sched_delete(h)
+    # flatten
+    sl_off = np.cumsum([0] + [r["seq"].size for r in steps]).astype(np.int32)
+    tb_all = [t for r in steps for t in r["tables"]]
+    tb_off = np.cumsum([0] + [t.size for t in tb_all]).astype(np.int32)
+    tok_off = np.cumsum([0] + [t.size for t in seq_tokens]).astype(np.int32)
+    np.savez_compressed(path, geometry=np.asarray([bs, num_blocks, max_seqs, budget, chunk], dtype=np.int32),
+                        slice_offset=sl_off, slice_seq=np.concatenate([r["seq"] for r in steps]),
+                        slice_start=np.concatenate([r["start"] for r in steps]), slice_len=np.concatenate([r["len"] for r in steps]),
+                        table_offset=tb_off, tables=np.concatenate(tb_all), seq_token_offset=tok_off,
+                        seq_tokens=np.concatenate(seq_tokens), scheduler_stats=st)
+    toks = int(sum(int(r["len"].sum()) for r in steps))
+    print(path, "steps", len(steps), "tokens", toks, "preemptions", int(st[1]), "admitted", int(st[2]), "finished", int(st[3]),
+          "bytes", os.path.getsize(path))
 
 
 def attention_case(ref, path, seed, q_heads, kv_heads, head_dim, bs, num_blocks, seq_ctx, seq_new):
@@ -146,6 +239,7 @@ def main():
                    seq_ctx=[33, 5, 16, 0], seq_new=[1, 9, 1, 20])
     allocator_trace(os.path.join(HERE, "allocator_trace.json"))
     casts(ref, os.path.join(HERE, "casts.json"))
+    engine_trace(ref, os.path.join(HERE, "engine_trace.npz"))
 
 
 if __name__ == "__main__":
