@@ -284,7 +284,9 @@ def run_ours(args, rank, local_rank, world):
         for l in range(L):
             layer(l, q_l[l], k_l[l], v_l[l], out_l[l])
 
-    launches_per_step = (2 if fused else 3) * L      # kernels: [append,] attention, merge
+    plan.build_host(idx.token_pos)
+    cluster_form = int(plan.plan.cluster)            # > 0: small-step form, the merge happens inside the attention launch
+    launches_per_step = ((2 if fused else 3) - (1 if cluster_form else 0)) * L      # kernels: [append,] attention [, merge]
 
     # ---- end-to-end step: host buffers in, host buffers out --------------------------
     # Host side: one pinned staging buffer per layer holding that layer's q | k | v rows back to back
@@ -570,6 +572,8 @@ def run_ours(args, rank, local_rank, world):
                                "planning (positions change every step in serving); `e2e` re-plans on the host every step",
                        "cpu_affinity": getattr(args, "affinity_note", None),
                        "append": "inside the attention launch (pkv_append_decode_attn_planned)" if fused else "separate launch (pkv_append)",
+                       "attention_form": (f"clusters of {cluster_form} blocks per (token, kv head), merge inside the launch (PKV_DECODE_CLUSTER=1)"
+                                          if cluster_form else "split-K units + merge launch"),
                        **({"layers_override": args.layers} if args.layers else {})},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
@@ -1162,6 +1166,22 @@ def secondary_measurements(args, pkv, wl, torch, dev, pools, w):
                               "append": ln["config"]["append"], "launch": ln["config"]["launch"]}
     except Exception as e:
         sec["cfg2_decode"] = {"error": repr(e)}
+    prev_env = None
+    try:
+        # the same step in its opt-in cluster form (one launch per layer: append, attention and merge)
+        prev_env = os.environ.get("PKV_DECODE_CLUSTER")
+        os.environ["PKV_DECODE_CLUSTER"] = "1"
+        ln = run_ours(a2, 0, dev.index, 1)
+        sec["cfg2_decode_cluster_form"] = {"value_tok_s": ln["value"], "us_per_layer_in_graph": ln["ms_per_step"] * 1e3 / ln["config"]["layers"],
+                                           "attention_us_per_launch_eager": ln["roofline"]["us_per_launch"],
+                                           "attention_form": ln["config"]["attention_form"]}
+    except Exception as e:
+        sec["cfg2_decode_cluster_form"] = {"error": repr(e)}
+    finally:
+        if prev_env is None:
+            os.environ.pop("PKV_DECODE_CLUSTER", None)
+        else:
+            os.environ["PKV_DECODE_CLUSTER"] = prev_env
     try:
         sec["mixed_step"] = measure_mixed_step(pkv, torch, dev)
     except Exception as e:

@@ -197,7 +197,16 @@ typedef struct pkv_decode_plan {
                      before pkv_decode_attn_planned_* gets tensor maps bounded by the pool, so that a wrong
                      block id reads zeros instead of memory beyond it (llm-engine's launcher signature
                      carries no pool size, which is why this is optional) */
-  int pad[3];
+  int cluster;    /* blocks per thread-block cluster (2..8) for the small-step form of the attention launch: one
+                     cluster per (token, kv head), the history cut into one range per warp of the cluster, the
+                     split-K merge done inside the launch through the cluster's shared memory -- one launch per
+                     layer and no workspace traffic.  0 = the ordinary form (split-K units + merge launch).
+                     pkv_decode_plan_host[_image] sets it only when the environment has PKV_DECODE_CLUSTER=1
+                     (read at every call) and the step qualifies: 16-bit K/V, head_dim 64, at most 8 query
+                     heads per kv head, every cluster resident at once, at most 256 keys per warp.  A caller
+                     may set or clear it; a launch the device cannot hold falls back to the ordinary form.
+                     No counterpart in llm-engine. */
+  int pad[2];
 } pkv_decode_plan;
 
 size_t pkv_decode_plan_staging_bytes(int n_tokens, int kv_heads);

@@ -25,7 +25,7 @@ class DecodePlan(C.Structure):
     """Mirror of struct pkv_decode_plan."""
     _fields_ = [("n_tokens", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int), ("head_dim", C.c_int),
                 ("chunk", C.c_int), ("n_items", C.c_int), ("exact", C.c_int), ("reserved", C.c_int),
-                ("num_blocks", C.c_int), ("pad", C.c_int * 3)]
+                ("num_blocks", C.c_int), ("cluster", C.c_int), ("pad", C.c_int * 2)]
 
 
 _vp, _i, _f, _sz, _u64 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_uint64

@@ -38,6 +38,8 @@ struct Tuning {
   int variant;       // ring depth / occupancy variant of the tensor-core kernel
   int use_tma;       // 1: TMA + warp-specialised kernel where the geometry allows (default)
   int max_extra_cap;
+  int cluster_max_keys;  // the cluster form of small steps is offered only while no warp would get more keys than this
+  int cluster_size;      // 0 = as many blocks per cluster as stay resident; otherwise at most this many
 };
 int env_int(const char* name, int dflt) {
   const char* e = std::getenv(name);
@@ -53,9 +55,20 @@ const Tuning& tuning() {
     x.variant = env_int("PKV_DECODE_VARIANT", 0);
     x.use_tma = env_int("PKV_DECODE_TMA", 1);
     x.max_extra_cap = 16384;
+    x.cluster_max_keys = env_int("PKV_DECODE_CLUSTER_MAX_KEYS", 256);
+    x.cluster_size = env_int("PKV_DECODE_CLUSTER_SIZE", 0);
     return x;
   }();
   return t;
+}
+
+// PKV_DECODE_CLUSTER=1: the host planner may choose the cluster form of the attention launch for small
+// steps (read at every planning call, so a process can switch it).  Off by default: inside a replayed
+// CUDA graph with programmatic dependent launch the ordinary two-launch form measured 3 % faster on the
+// step it is meant for; launched eagerly, or without programmatic launch, the cluster form is 6 % faster.
+bool cluster_form_enabled() {
+  const char* e = std::getenv("PKV_DECODE_CLUSTER");
+  return e && e[0] == '1';
 }
 
 int max_extra(int kv_heads) { return (tuning().max_extra_cap + kv_heads - 1) / kv_heads; }
@@ -343,6 +356,72 @@ int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
   return check_launch("decode_tma_kernel");
 }
 
+// Small steps as thread-block clusters (decode_tma_kernel with CLUSTER): one cluster of `cs` blocks
+// per (token, kv head), merge inside the launch.  *launched stays false, with nothing enqueued, when
+// this device cannot hold all the clusters at once (they would queue behind one another): the
+// caller then takes the ordinary path.
+template <typename T, bool FUSED>
+int launch_tma_cluster_impl(const DecodeArgs& a, int cs, cudaStream_t stream, bool* launched) {
+  constexpr int WARPS = 4;
+  using S = TmaSmem<64, 2, 2, WARPS>;
+  auto kern = decode_tma_kernel<T, 64, 1, 2, 2, WARPS, 3, 1, FUSED, true>;
+  *launched = false;
+  const long long pairs = static_cast<long long>(a.n_tokens) * a.kv_heads;
+  if (cs < 2 || cs > 8 || pairs * cs > 0x7fffffffll) return PKV_OK;
+  static thread_local int configured_device = -1;
+  static thread_local int max_clusters[9];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve %d bytes of shared memory: %s", S::kBytes, cudaGetErrorString(e));
+    for (int i = 0; i < 9; ++i) max_clusters[i] = -1;
+    configured_device = dev;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(pairs * cs));
+  cfg.blockDim = dim3(WARPS * 32);
+  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(cs);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  if (max_clusters[cs] < 0) {
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    max_clusters[cs] = n;
+  }
+  if (pairs > max_clusters[cs]) return PKV_OK;
+  alignas(64) CUtensorMap kmap, vmap;
+  constexpr bool is_bf16 = !std::is_same<T, __half>::value;
+  const int kv_dim = a.kv_heads * a.head_dim;
+  int st = make_pool_tensor_map(&kmap, a.k_cache, is_bf16, kv_dim, 16, a.pool_rows);
+  if (st != PKV_OK) return st;
+  st = make_pool_tensor_map(&vmap, a.v_cache, is_bf16, kv_dim, 16, a.pool_rows);
+  if (st != PKV_OK) return st;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, kern, a, kmap, vmap);
+  *launched = true;
+  return check_launch("decode_tma_kernel (clusters)");
+}
+
+template <typename T>
+int launch_tma_cluster(const DecodeArgs& a, int cs, cudaStream_t stream, bool* launched) {
+  *launched = false;
+  if constexpr (IsF32<T>::value) {
+    return PKV_OK;
+  } else {
+    if (a.new_k != nullptr) return launch_tma_cluster_impl<T, true>(a, cs, stream, launched);
+    return launch_tma_cluster_impl<T, false>(a, cs, stream, launched);
+  }
+}
+
 template <typename T, int DJ>
 int launch_simt(const DecodeArgs& a, int grid, cudaStream_t stream) {
   const size_t smem = simt_smem_bytes<T>(a.head_dim);
@@ -628,6 +707,11 @@ int decode_planned(const pkv_decode_plan* plan, const void* q, const void* kc, c
     a.shared_items = reinterpret_cast<const int4*>(a.items + plan->n_items);
     a.n_shared = n_shared;
   }
+  if (plan->cluster >= 2 && !peers && n_shared == 0 && a.head_dim == 64 && a.group <= 8 && tma_path<T>(a)) {
+    bool launched = false;
+    st = launch_tma_cluster<T>(a, plan->cluster, static_cast<cudaStream_t>(stream), &launched);
+    if (st != PKV_OK || launched) return st;
+  }
   long long blocks = static_cast<long long>(plan->n_items) * plan->kv_heads;
   if (!plan->exact && blocks > persistent_grid()) blocks = persistent_grid();
   if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
@@ -839,6 +923,21 @@ static int plan_host_image(const char* fn, const int* h_token_pos, int n_tokens,
   plan->n_items = ni;
   plan->exact = 1;
   plan->reserved = np > 0 ? 1 : 0;       // whether any token was split (the merge kernel is skipped otherwise)
+  // Small steps: when every (token, kv head) can have a cluster of its own with all clusters resident at
+  // once, and no warp of a cluster would get more than a few slabs, the attention call runs as clusters
+  // and merges inside the launch (the image above stays valid: the call falls back to it if the device
+  // turns the cluster launch down).
+  if (cluster_form_enabled() && np > 0 && head_dim == 64 && q_heads / kv_heads <= 8) {
+    const long long pairs = static_cast<long long>(n_tokens) * kv_heads;
+    const long long resident = static_cast<long long>(persistent_sms()) * 3;
+    if (pairs * 2 <= resident) {
+      int cs = static_cast<int>(std::min<long long>(8, resident / pairs));
+      if (tuning().cluster_size >= 2 && tuning().cluster_size < cs) cs = tuning().cluster_size;
+      int max_len = 0;
+      for (int t = 0; t < n_tokens; ++t) max_len = std::max(max_len, h_token_pos[t] + 1);
+      if ((max_len + 4 * cs - 1) / (4 * cs) <= tuning().cluster_max_keys) plan->cluster = cs;
+    }
+  }
   return PKV_OK;
 }
 

@@ -61,13 +61,43 @@ template <int D, int MT, int NSTAGES, int WARPS> struct TmaSmem {
 // FUSED_APPEND: the unit that reaches a token's newest key takes that row from the step's k / v
 // inputs and writes it to the pool (DecodeArgs::new_k); a separate instantiation, so that the
 // plain kernel carries none of it.
-template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS, int TOK = 1, bool FUSED_APPEND = false>
+// CLUSTER: small steps.  The launch is a grid of thread-block clusters, one cluster per (token, kv
+// head); the history is cut into as many equal ranges as the cluster has warps (fewer when it is
+// short), warp w of block r takes range w * blocks + r, and the split-K merge happens inside the
+// launch: every warp leaves its partial in its own shared memory, the cluster meets on its
+// hardware barrier, and all its threads fold the partials -- read from one another's shared memory
+// -- into the output row.  No plan, no workspace, no merge kernel; the ranges follow from
+// token_pos alone.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float2 cluster_ld2(uint32_t cluster_addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 cluster_ld4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS, int TOK = 1, bool FUSED_APPEND = false,
+          bool CLUSTER = false>
 __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     decode_tma_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap kmap,
                       const __grid_constant__ CUtensorMap vmap) {
   using S = TmaSmem<D, MT, NSTAGES, WARPS>;
   static_assert(TOK == 1 || TOK == 4, "a shared unit holds four tokens");
   static_assert(NT % TOK == 0, "whole head tiles per token");
+  static_assert(!CLUSTER || TOK == 1, "cluster launches take ordinary tokens");
+  static_assert(!CLUSTER || (8 * NT * D + 32 * NT) * 4 <= S::kWarpBytes, "a warp's partial must fit its ring");
   constexpr int NTG = NT / TOK;   // head tiles (8 heads each) per token
   constexpr int KS = D / 16;
   constexpr int HALVES = S::kHalves;
@@ -106,9 +136,26 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(&vmap) : "memory");
   }
   bool waited = false;
-  const int n_items = TOK > 1 ? a.n_shared : (a.direct ? a.n_tokens : a.header->n_items);
-  const int total = n_items * a.kv_heads;
-  const int gw = blockIdx.x * WARPS + warp, GW = gridDim.x * WARPS;
+  // Cluster launches: this warp's one unit, from the token's position alone (a step constant).
+  int c_token = 0, c_kvh = 0, c_begin = 0, c_len = 0, c_nsplits = 1, c_split = 0;
+  uint32_t c_rank = 0, c_size = 1;
+  if constexpr (CLUSTER) {
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(c_rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(c_size));
+    const int pair = blockIdx.x / c_size;                  // clusters are runs of consecutive blocks
+    c_token = pair / a.kv_heads;
+    c_kvh = pair - c_token * a.kv_heads;
+    const int len = max(__ldg(a.token_pos + c_token), 0) + 1;
+    const int nw = WARPS * static_cast<int>(c_size);
+    const int range = (((len + nw - 1) / nw + SLAB - 1) / SLAB) * SLAB;   // whole slabs per warp
+    c_nsplits = (len + range - 1) / range;
+    c_split = warp * static_cast<int>(c_size) + static_cast<int>(c_rank);   // neighbouring ranges on different SMs
+    c_begin = c_split * range;
+    c_len = min(range, len - c_begin);                     // <= 0: no unit for this warp
+  }
+  const int n_items = CLUSTER ? 0 : (TOK > 1 ? a.n_shared : (a.direct ? a.n_tokens : a.header->n_items));
+  const int total = CLUSTER ? (c_len > 0 ? 1 : 0) : n_items * a.kv_heads;
+  const int gw = CLUSTER ? 0 : blockIdx.x * WARPS + warp, GW = CLUSTER ? 1 : gridDim.x * WARPS;
 
   // ---------------------------- issue side ----------------------------
   int iu = gw - GW;             // unit the issue pointer is in (advanced before first use)
@@ -122,9 +169,14 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     while (i_slab >= i_nslabs) {
       iu += GW;
       if (iu >= total) { iu = total; return false; }
-      const int item = iu / a.kv_heads, kvh = iu - item * a.kv_heads;
+      const int item = iu / a.kv_heads, kvh = CLUSTER ? c_kvh : iu - item * a.kv_heads;
       int token, part;
-      if constexpr (TOK > 1) {
+      if constexpr (CLUSTER) {
+        token = c_token;
+        i_kvbeg = c_begin;
+        i_len = c_len;
+        part = 0;
+      } else if constexpr (TOK > 1) {
         const int4 h0 = __ldg(a.shared_items + 3 * item), tk = __ldg(a.shared_items + 3 * item + 1);
         i_kvbeg = h0.x;
         i_len = h0.y;
@@ -194,10 +246,14 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   const int mi = lane >> 3, r8 = lane & 7;
   bool more = true;
   for (int cu = gw; cu < total; cu += GW) {
-    const int item = cu / a.kv_heads, kvh = cu - item * a.kv_heads;
+    const int item = cu / a.kv_heads, kvh = CLUSTER ? c_kvh : cu - item * a.kv_heads;
     int token, kv_begin, kv_len, part;
     int toks[TOK], parts[TOK], n_tok = 1;
-    if constexpr (TOK > 1) {
+    if constexpr (CLUSTER) {
+      token = c_token; kv_begin = c_begin; kv_len = c_len;
+      part = c_nsplits > 1 ? c_split : -1;
+      toks[0] = token; parts[0] = part;
+    } else if constexpr (TOK > 1) {
       const int4 h0 = __ldg(a.shared_items + 3 * item), tk = __ldg(a.shared_items + 3 * item + 1),
                  pt = __ldg(a.shared_items + 3 * item + 2);
       kv_begin = h0.x; kv_len = h0.y; n_tok = h0.z;
@@ -374,7 +430,9 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
       }
       ++n_consumed;
     }
-    if (!ok) return;  // this warp has copies in flight only into its own ring; nothing else depends on it
+    if constexpr (!CLUSTER) {
+      if (!ok) return;  // this warp has copies in flight only into its own ring; nothing else depends on it
+    }                   // (in a cluster the warp stays for the barriers; its give-up is on record)
 
     while (more && n_issued - n_consumed < NSTAGES) more = issue_next();  // keep loads flowing through the finish
 
@@ -412,8 +470,12 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
       for (int nt = 0; nt < NT; ++nt) {
         const int ti = nt / NTG;
         if (ti >= n_tok) continue;
-        float* pacc = a.part_acc + (static_cast<size_t>(parts[ti]) * a.q_heads + head_base) * D;
-        float* pml = a.part_ml + (static_cast<size_t>(parts[ti]) * a.q_heads + head_base) * 2;
+        // the partial: to the workspace, or (cluster launches) to the start of this warp's own ring,
+        // which holds no copy in flight any more -- [8 NT heads][D] sums, then (maximum, sum) per head
+        float* pacc = CLUSTER ? reinterpret_cast<float*>(ring_ptr)
+                              : a.part_acc + (static_cast<size_t>(parts[ti]) * a.q_heads + head_base) * D;
+        float* pml = CLUSTER ? reinterpret_cast<float*>(ring_ptr) + 8 * NT * D
+                             : a.part_ml + (static_cast<size_t>(parts[ti]) * a.q_heads + head_base) * 2;
         const int h0 = 8 * (nt % NTG) + 2 * c;
 #pragma unroll
         for (int dm = 0; dm < KS; ++dm) {
@@ -432,6 +494,53 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
           if (h0 + 1 < a.group) { pml[2 * h0 + 2] = m_run[nt][1] * sl2; pml[2 * h0 + 3] = l_run[nt][1]; }
         }
       }
+    }
+  }
+  if constexpr (CLUSTER) {
+    if (c_nsplits > 1) {               // the same for every thread of the cluster
+      cluster_sync_all();              // every warp's partial is in its shared memory
+      const int CT = static_cast<int>(c_size) * WARPS * 32, ct = static_cast<int>(c_rank) * WARPS * 32 + threadIdx.x;
+      const int n4 = a.group * D / 4;  // groups of four neighbouring dims of the (token, kv head)'s output rows
+      for (int e4 = ct; e4 < n4; e4 += CT) {
+        const int h = (4 * e4) / D, d = 4 * e4 - h * D;
+        constexpr int B = 16;          // one round of loads for up to 16 ranges
+        float m_run = -INFINITY, l_run = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < c_nsplits; s0 += B) {
+          float2 ml[B];
+          float4 v[B];
+#pragma unroll
+          for (int i = 0; i < B; ++i) {
+            const int sp = s0 + i;
+            if (sp < c_nsplits) {
+              const uint32_t w_owner = static_cast<uint32_t>(sp) / c_size, r_owner = static_cast<uint32_t>(sp) - w_owner * c_size;
+              const uint32_t base = cluster_map(ring0 + w_owner * S::kWarpBytes, r_owner);
+              ml[i] = cluster_ld2(base + static_cast<uint32_t>(8 * NT * D + 2 * h) * 4u);
+              v[i] = cluster_ld4(base + static_cast<uint32_t>(h * D + d) * 4u);
+            } else {
+              ml[i] = make_float2(-INFINITY, 0.f);
+              v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          float mb = m_run;
+#pragma unroll
+          for (int i = 0; i < B; ++i) mb = fmaxf(mb, ml[i].x);
+          const float f0 = (m_run == -INFINITY) ? 0.f : exp2f(m_run - mb);
+          l_run *= f0;
+          acc.x *= f0; acc.y *= f0; acc.z *= f0; acc.w *= f0;
+#pragma unroll
+          for (int i = 0; i < B; ++i) {
+            const float f = (ml[i].x == -INFINITY) ? 0.f : exp2f(ml[i].x - mb);
+            l_run += f * ml[i].y;
+            acc.x += f * v[i].x; acc.y += f * v[i].y; acc.z += f * v[i].z; acc.w += f * v[i].w;
+          }
+          m_run = mb;
+        }
+        const float inv = 1.f / l_run;
+        T* o = out_row<T>(a, a.out, c_token) + static_cast<size_t>(c_kvh * a.group + h) * D + d;
+        *reinterpret_cast<uint2*>(o) = make_uint2(pack2<T>(acc.x * inv, acc.y * inv), pack2<T>(acc.z * inv, acc.w * inv));
+      }
+      cluster_sync_all();              // nobody leaves while its shared memory is still being read
     }
   }
 }

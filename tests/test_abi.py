@@ -107,6 +107,38 @@ def test_host_plan_layout_without_a_device(pkv):
     assert st == pkv._lib.PKV_E_ARG and b"negative" in L.pkv_last_error()
 
 
+def test_host_planner_offers_the_cluster_form_only_on_request(pkv, monkeypatch):
+    """pkv_decode_plan.cluster: set by the host planner only with PKV_DECODE_CLUSTER=1 in the environment
+    (read at every call), only for steps whose (token, kv head) pairs can each have a resident cluster
+    (3 blocks on each of the device's SMs; 148 assumed without a device) with at most 256 keys per warp,
+    head_dim 64 and at most 8 query heads per kv head."""
+    L = pkv.lib()
+
+    def cluster_of(pos, qh, kvh, hd=64):
+        pos = np.asarray(pos, dtype=np.int32)
+        nstage = L.pkv_decode_plan_staging_bytes(pos.size, kvh)
+        staging = np.zeros(nstage, dtype=np.uint8)
+        plan = pkv._lib.DecodePlan()
+        image = C.c_size_t(0)
+        ws = L.pkv_decode_workspace_bytes(pos.size, qh, kvh, hd)
+        st = L.pkv_decode_plan_host_image(pos.ctypes.data, pos.size, qh, kvh, hd, staging.ctypes.data, nstage, ws,
+                                          C.byref(plan), C.byref(image))
+        assert st == 0, L.pkv_last_error()
+        return plan.cluster
+
+    monkeypatch.delenv("PKV_DECODE_CLUSTER", raising=False)
+    assert cluster_of([1000] * 8, 32, 4) == 0
+    monkeypatch.setenv("PKV_DECODE_CLUSTER", "1")
+    assert cluster_of([1000] * 8, 32, 4) == 8            # 32 pairs: the largest portable cluster
+    assert cluster_of([1000] * 64, 14, 2) == 3           # 128 pairs on 444 block slots
+    assert cluster_of([1000] * 111, 14, 2) == 2          # 222 pairs
+    assert cluster_of([1000] * 112, 14, 2) == 0          # 224 pairs: two blocks each would not all be resident
+    assert cluster_of([20000] * 8, 32, 4) == 0           # 626 keys per warp
+    assert cluster_of([1000] * 8, 32, 2) == 0            # 16 query heads per kv head
+    assert cluster_of([1000] * 8, 32, 4, hd=128) == 0
+    assert cluster_of([100] * 8, 32, 4) == 0             # nothing to merge: no token is split
+
+
 def test_step_pack_matches_restatement(pkv, orc):
     import ctypes
     rng = np.random.default_rng(4)

@@ -1,0 +1,90 @@
+"""GPU parity for the small-step form of the decode attention: one thread-block cluster per (token,
+kv head), the history cut into one range per warp of the cluster, split-K merge inside the launch
+through the cluster's shared memory (decode_tma_kernel with CLUSTER).  The host planner chooses it
+(pkv_decode_plan.cluster); results must match the CPU checker exactly as the ordinary form does."""
+import numpy as np
+import pytest
+
+from tests.gpu_util import Case, check_case, from_device
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _cluster_form_on(monkeypatch):
+    """The cluster form is opt-in (PKV_DECODE_CLUSTER=1, read at every planning call)."""
+    monkeypatch.setenv("PKV_DECODE_CLUSTER", "1")
+
+
+def _nb(ctx, bs):
+    return sum((c + 1 + bs - 1) // bs for c in ctx) + 16
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("mode", ["host_plan", "fused_append"])
+@pytest.mark.parametrize("shape", [
+    # q_heads, kv_heads, block_size, contexts (positions of the one new token per sequence)
+    (14, 2, 16, [300, 700, 1100, 1500, 1900, 2047, 256, 999]),        # 16 pairs: clusters of 8, up to 32 ranges
+    (32, 4, 16, [64, 65, 127, 128, 129, 1023, 1024, 1025] * 4),        # 128 pairs: clusters of 3
+    (8, 8, 32, [33, 200, 511]),                                        # one query head per kv head, block 32
+    (16, 2, 16, [31, 32, 33, 63, 64, 95, 96, 97, 255, 256, 257]),      # range edges on slab boundaries
+])
+def test_cluster_form_matches_checker(pkv, orc, torch_cuda, dtype, mode, shape):
+    qh, kvh, bs, ctx = shape
+    case = Case(orc, dtype, qh, kvh, 64, bs, _nb(ctx, bs), ctx, [1] * len(ctx), 77, pkv)
+    want = case.expected(orc)
+    d = case.run_gpu(pkv, torch_cuda, mode)
+    assert d["plan"].plan.cluster >= 2, "the planner was expected to choose the cluster form for this step"
+    check_case(case, pkv, torch_cuda, orc, mode)
+    del want
+
+
+def test_cluster_form_agrees_with_ordinary_form(pkv, orc, torch_cuda):
+    """Same step through both forms (the caller may clear pkv_decode_plan.cluster): the outputs agree to
+    rounding of the 16-bit result (the keys are grouped differently), both within tolerance of the checker."""
+    ctx = [int(x) for x in np.random.default_rng(5).integers(256, 2049, size=40)]
+    case = Case(orc, "bf16", 14, 2, 64, 16, _nb(ctx, 16), ctx, [1] * len(ctx), 11, pkv)
+    _, _, want = case.expected(orc)
+    d = case.upload(torch_cuda)
+    pkv.launch_store_kv(d["k"], d["v"], d["slots"], d["kc"], d["vc"], case.N, case.kvh * case.hd)
+    args = (d["q"], d["kc"], d["vc"], d["block_tables"], d["table_offset"], d["token_seq"], d["token_pos"])
+    plan = pkv.DecodePlan(case.N, case.qh, case.kvh, case.hd).build_host(case.idx.token_pos)
+    assert plan.plan.cluster >= 2
+    out_c = torch_cuda.zeros_like(d["out"])
+    plan.attention(*args, out_c, case.bs, case.scale)
+    plan.plan.cluster = 0
+    out_o = torch_cuda.zeros_like(d["out"])
+    plan.attention(*args, out_o, case.bs, case.scale)
+    torch_cuda.cuda.synchronize()
+    _, got_c = from_device(torch_cuda, orc, out_c, "bf16")
+    _, got_o = from_device(torch_cuda, orc, out_o, "bf16")
+    assert np.abs(got_c - got_o).max() <= 2e-2 * np.abs(want).max()
+    assert np.abs(got_c - want.reshape(got_c.shape)).max() <= 2e-2 * np.abs(want).max()
+    assert pkv.debug_device_flags() == 0
+
+
+def test_planner_keeps_the_ordinary_form_for_large_or_long_steps(pkv, torch_cuda, monkeypatch):
+    """More (token, kv head) pairs than can each have a resident cluster, or histories too long for a
+    cluster's warps: the plan says 0 and the ordinary split-K launch runs.  Likewise without the switch."""
+    many = pkv.DecodePlan(256, 32, 4, 64).build_host(np.full(256, 1000, dtype=np.int32))
+    assert many.plan.cluster == 0
+    long_ctx = pkv.DecodePlan(8, 32, 4, 64).build_host(np.full(8, 20000, dtype=np.int32))
+    assert long_ctx.plan.cluster == 0
+    wide = pkv.DecodePlan(8, 32, 2, 64).build_host(np.full(8, 1000, dtype=np.int32))   # 16 query heads per kv head
+    assert wide.plan.cluster == 0
+    small = pkv.DecodePlan(8, 32, 4, 64).build_host(np.full(8, 1000, dtype=np.int32))
+    assert small.plan.cluster == 8
+    monkeypatch.delenv("PKV_DECODE_CLUSTER")
+    off = pkv.DecodePlan(8, 32, 4, 64).build_host(np.full(8, 1000, dtype=np.int32))
+    assert off.plan.cluster == 0
+
+
+def test_configuration_2_at_full_size_through_clusters(pkv, orc, torch_cuda, workloads):
+    """Configuration 2 (64 sequences, contexts 256..2,048, 14 query / 2 kv heads, bf16): the step the
+    cluster form is meant for, with the append inside the launch, at full size."""
+    w = workloads.make("cfg2", layers=1)
+    ctx = [int(c) for c in w.ctx]
+    case = Case(orc, "bf16", w.q_heads, w.kv_heads, w.head_dim, w.block_size, w.num_blocks, ctx, [1] * len(ctx), 1235, pkv)
+    d = case.run_gpu(pkv, torch_cuda, "fused_append")
+    assert d["plan"].plan.cluster == 3
+    check_case(case, pkv, torch_cuda, orc, "fused_append")
