@@ -572,7 +572,7 @@ def run_ours(args, rank, local_rank, world):
                                "planning (positions change every step in serving); `e2e` re-plans on the host every step",
                        "cpu_affinity": getattr(args, "affinity_note", None),
                        "append": "inside the attention launch (pkv_append_decode_attn_planned)" if fused else "separate launch (pkv_append)",
-                       "attention_form": (f"clusters of {cluster_form} blocks per (token, kv head), merge inside the launch (PKV_DECODE_CLUSTER=1)"
+                       "attention_form": (f"clusters of {cluster_form} blocks per (token, kv head), merge inside the launch"
                                           if cluster_form else "split-K units + merge launch"),
                        **({"layers_override": args.layers} if args.layers else {})},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
@@ -1163,20 +1163,21 @@ def secondary_measurements(args, pkv, wl, torch, dev, pools, w):
         sec["cfg2_decode"] = {"value_tok_s": ln["value"], "ms_per_step": ln["ms_per_step"], "us_per_layer_in_graph": ln["ms_per_step"] * 1e3 / ln["config"]["layers"],
                               "step_hbm_gbs": ln["step_hbm_gbs"], "frac_of_peak_whole_step": ln["step_hbm_gbs"] / r["peak"],
                               "attention_us_per_launch_eager": r["us_per_launch"], "attention_frac_eager": r["frac"],
-                              "append": ln["config"]["append"], "launch": ln["config"]["launch"]}
+                              "append": ln["config"]["append"], "launch": ln["config"]["launch"],
+                              "attention_form": ln["config"]["attention_form"]}
     except Exception as e:
         sec["cfg2_decode"] = {"error": repr(e)}
     prev_env = None
     try:
-        # the same step in its opt-in cluster form (one launch per layer: append, attention and merge)
+        # the same step with the cluster form switched off: append + attention, then the merge launch
         prev_env = os.environ.get("PKV_DECODE_CLUSTER")
-        os.environ["PKV_DECODE_CLUSTER"] = "1"
+        os.environ["PKV_DECODE_CLUSTER"] = "0"
         ln = run_ours(a2, 0, dev.index, 1)
-        sec["cfg2_decode_cluster_form"] = {"value_tok_s": ln["value"], "us_per_layer_in_graph": ln["ms_per_step"] * 1e3 / ln["config"]["layers"],
+        sec["cfg2_decode_ordinary_form"] = {"value_tok_s": ln["value"], "us_per_layer_in_graph": ln["ms_per_step"] * 1e3 / ln["config"]["layers"],
                                            "attention_us_per_launch_eager": ln["roofline"]["us_per_launch"],
                                            "attention_form": ln["config"]["attention_form"]}
     except Exception as e:
-        sec["cfg2_decode_cluster_form"] = {"error": repr(e)}
+        sec["cfg2_decode_ordinary_form"] = {"error": repr(e)}
     finally:
         if prev_env is None:
             os.environ.pop("PKV_DECODE_CLUSTER", None)

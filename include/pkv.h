@@ -78,6 +78,10 @@ const char* pkv_last_error(void);
  * No llm-engine counterparts. */
 int pkv_debug_device_flags(unsigned int* flags);
 int pkv_debug_set_reported_flags(unsigned int flags);
+/* How many attention launches of this process took the cluster form (pkv_decode_plan.cluster): a
+ * plan that asks for it on a device that cannot hold all the clusters at once silently takes the
+ * ordinary form, and this counter is how a test tells the two apart.  No llm-engine counterpart. */
+unsigned long long pkv_debug_cluster_launches(void);
 
 /* ----------------------------------------------------------- K/V append ----
  * K/V append.  Replaces engine::launch_store_kv (include/engine/cuda_kernels.h:43-45,
@@ -201,10 +205,11 @@ typedef struct pkv_decode_plan {
                      cluster per (token, kv head), the history cut into one range per warp of the cluster, the
                      split-K merge done inside the launch through the cluster's shared memory -- one launch per
                      layer and no workspace traffic.  0 = the ordinary form (split-K units + merge launch).
-                     pkv_decode_plan_host[_image] sets it only when the environment has PKV_DECODE_CLUSTER=1
-                     (read at every call) and the step qualifies: 16-bit K/V, head_dim 64, at most 8 query
-                     heads per kv head, every cluster resident at once, at most 256 keys per warp.  A caller
-                     may set or clear it; a launch the device cannot hold falls back to the ordinary form.
+                     pkv_decode_plan_host[_image] sets it (to 2, 3, 4 or 8) when the step qualifies -- head_dim 64,
+                     at most 8 query heads per kv head, every cluster resident at once, at most 256 keys per
+                     warp -- unless the environment has PKV_DECODE_CLUSTER=0 (read at every call); the other
+                     planners leave 0.  A caller may clear it; a launch the kernel or the device cannot take
+                     (fp32 K/V, block_size < 16, clusters that would not all be resident) runs the ordinary form.
                      No counterpart in llm-engine. */
   int pad[2];
 } pkv_decode_plan;

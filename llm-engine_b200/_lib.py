@@ -37,6 +37,7 @@ SIGNATURES = {
     "pkv_last_error": (C.c_char_p, []),
     "pkv_debug_device_flags": (_i, [_vp]),
     "pkv_debug_set_reported_flags": (_i, [C.c_uint]),
+    "pkv_debug_cluster_launches": (C.c_ulonglong, []),
     "pkv_mixed_attn_workspace_bytes": (_sz, [_i] * 4),
     **{f"pkv_mixed_attn_{s}": (_i, [_vp] * 8 + [_i] * 6 + [_f, _i, _vp, _sz, _vp]) for s in ("f16", "bf16")},
     **{f"pkv_append_{s}": (_i, [_vp] * 5 + [_i, _i, _vp]) for s in ("f16", "bf16", "f32")},

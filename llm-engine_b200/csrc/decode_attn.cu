@@ -1,6 +1,7 @@
 // C-ABI entry points for paged decode attention (include/pkv.h, "decode attention"):
 // argument validation, split-K planning (host and device), kernel selection.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <type_traits>
 #include <cstring>
@@ -62,13 +63,13 @@ const Tuning& tuning() {
   return t;
 }
 
-// PKV_DECODE_CLUSTER=1: the host planner may choose the cluster form of the attention launch for small
-// steps (read at every planning call, so a process can switch it).  Off by default: inside a replayed
-// CUDA graph with programmatic dependent launch the ordinary two-launch form measured 3 % faster on the
-// step it is meant for; launched eagerly, or without programmatic launch, the cluster form is 6 % faster.
+// PKV_DECODE_CLUSTER=0: the host planner never chooses the cluster form of the attention launch for small
+// steps (read at every planning call, so a process can switch it).  On by default: on the step it is
+// meant for (64 sequences, 256-2,048 keys) it is 8 % faster than the two ordinary launches inside a
+// replayed graph and 20 % faster launched eagerly.
 bool cluster_form_enabled() {
   const char* e = std::getenv("PKV_DECODE_CLUSTER");
-  return e && e[0] == '1';
+  return !(e && e[0] == '0');
 }
 
 int max_extra(int kv_heads) { return (tuning().max_extra_cap + kv_heads - 1) / kv_heads; }
@@ -356,6 +357,8 @@ int launch_tma(const DecodeArgs& a, int grid, cudaStream_t stream) {
   return check_launch("decode_tma_kernel");
 }
 
+std::atomic<unsigned long long> g_cluster_launches{0};   // pkv_debug_cluster_launches
+
 // Small steps as thread-block clusters (decode_tma_kernel with CLUSTER): one cluster of `cs` blocks
 // per (token, kv head), merge inside the launch.  *launched stays false, with nothing enqueued, when
 // this device cannot hold all the clusters at once (they would queue behind one another): the
@@ -367,21 +370,22 @@ int launch_tma_cluster_impl(const DecodeArgs& a, int cs, cudaStream_t stream, bo
   auto kern = decode_tma_kernel<T, 64, 1, 2, 2, WARPS, 3, 1, FUSED, true>;
   *launched = false;
   const long long pairs = static_cast<long long>(a.n_tokens) * a.kv_heads;
-  if (cs < 2 || cs > 8 || pairs * cs > 0x7fffffffll) return PKV_OK;
+  if (!cluster_size_ok(cs) || pairs * cs > 0x7fffffffll) return PKV_OK;
+  constexpr int kSmem = S::kBytes + kClusterLandBytes;
   static thread_local int configured_device = -1;
   static thread_local int max_clusters[9];
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
-    if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve %d bytes of shared memory: %s", S::kBytes, cudaGetErrorString(e));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return fail(PKV_E_CUDA, "decode: cannot reserve %d bytes of shared memory: %s", kSmem, cudaGetErrorString(e));
     for (int i = 0; i < 9; ++i) max_clusters[i] = -1;
     configured_device = dev;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(pairs * cs));
   cfg.blockDim = dim3(WARPS * 32);
-  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.dynamicSmemBytes = kSmem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -408,6 +412,7 @@ int launch_tma_cluster_impl(const DecodeArgs& a, int cs, cudaStream_t stream, bo
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaLaunchKernelEx(&cfg, kern, a, kmap, vmap);
   *launched = true;
+  g_cluster_launches.fetch_add(1, std::memory_order_relaxed);
   return check_launch("decode_tma_kernel (clusters)");
 }
 
@@ -933,6 +938,7 @@ static int plan_host_image(const char* fn, const int* h_token_pos, int n_tokens,
     if (pairs * 2 <= resident) {
       int cs = static_cast<int>(std::min<long long>(8, resident / pairs));
       if (tuning().cluster_size >= 2 && tuning().cluster_size < cs) cs = tuning().cluster_size;
+      while (cs > 2 && !cluster_size_ok(cs)) --cs;       // 8, 4, 3 or 2 blocks: what the landing areas are sized for
       int max_len = 0;
       for (int t = 0; t < n_tokens; ++t) max_len = std::max(max_len, h_token_pos[t] + 1);
       if ((max_len + 4 * cs - 1) / (4 * cs) <= tuning().cluster_max_keys) plan->cluster = cs;
@@ -1240,6 +1246,8 @@ PKV_DECODE_PEER_ENTRY(bf16, __nv_bfloat16)
 
 PKV_APPEND_DECODE_ENTRY(f16, __half)
 PKV_APPEND_DECODE_ENTRY(bf16, __nv_bfloat16)
+
+unsigned long long pkv_debug_cluster_launches(void) { return pkv::g_cluster_launches.load(std::memory_order_relaxed); }
 
 size_t pkv_mixed_attn_workspace_bytes(int n_tokens, int q_heads, int kv_heads, int head_dim) {
   if (n_tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0) return 0;

@@ -64,28 +64,29 @@ template <int D, int MT, int NSTAGES, int WARPS> struct TmaSmem {
 // CLUSTER: small steps.  The launch is a grid of thread-block clusters, one cluster per (token, kv
 // head); the history is cut into as many equal ranges as the cluster has warps (fewer when it is
 // short), warp w of block r takes range w * blocks + r, and the split-K merge happens inside the
-// launch: every warp leaves its partial in its own shared memory, the cluster meets on its
-// hardware barrier, and all its threads fold the partials -- read from one another's shared memory
-// -- into the output row.  No plan, no workspace, no merge kernel; the ranges follow from
-// token_pos alone.
+// launch.  Block r of the cluster owns query heads r, r + blocks, ... of the group: a warp that has
+// finished its range sends, for every head, that head's 64 sums and (maximum, sum) to the head's
+// owner -- st.async stores into the owner's landing area in shared memory, each completing bytes
+// on the owner's mbarrier -- and every block, once its barrier has counted all the bytes its heads
+// expect, folds them from its own shared memory into the output rows.  No plan, no workspace, no
+// merge kernel, no cluster-wide barrier after the first (which only publishes the mbarriers): the
+// ranges and the byte counts follow from token_pos alone.
+constexpr int kClusterRecord = 68 * 4;   // one (head, range) record in a landing area: 64 sums, maximum, sum, 8 bytes unused
+// Landing area of a block: records for ceil(8 / blocks) heads x (4 warps x blocks) ranges; the
+// cluster sizes the launcher offers (2, 3, 4, 8) need at most 3 x 12 of them.
+constexpr int kClusterLandBytes = 36 * kClusterRecord + 96;
+__host__ __device__ constexpr bool cluster_size_ok(int cs) { return cs == 2 || cs == 3 || cs == 4 || cs == 8; }
+
 __device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ float2 cluster_ld2(uint32_t cluster_addr) {
-  float2 v;
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 cluster_ld4(uint32_t cluster_addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+// 16 bytes into another block's shared memory; the bytes count on that block's mbarrier when they land.
+__device__ __forceinline__ void cluster_push4(uint32_t dst_cluster_addr, float4 v, uint32_t bar_cluster_addr) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];\n" ::"r"(dst_cluster_addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(bar_cluster_addr)
+               : "memory");
 }
 
 template <typename T, int D, int NT, int MT, int NSTAGES, int WARPS, int MIN_BLOCKS, int TOK = 1, bool FUSED_APPEND = false,
@@ -97,6 +98,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   static_assert(TOK == 1 || TOK == 4, "a shared unit holds four tokens");
   static_assert(NT % TOK == 0, "whole head tiles per token");
   static_assert(!CLUSTER || TOK == 1, "cluster launches take ordinary tokens");
+  static_assert(!CLUSTER || (NT == 1 && D == 64), "the cluster form is written for up to 8 heads of 64 dims per kv head");
   static_assert(!CLUSTER || (8 * NT * D + 32 * NT) * 4 <= S::kWarpBytes, "a warp's partial must fit its ring");
   constexpr int NTG = NT / TOK;   // head tiles (8 heads each) per token
   constexpr int KS = D / 16;
@@ -106,6 +108,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long full_bar[WARPS * NSTAGES];
+  __shared__ __align__(8) unsigned long long land_bar;     // cluster launches: counts the bytes this block's heads expect
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -152,6 +155,20 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     c_split = warp * static_cast<int>(c_size) + static_cast<int>(c_rank);   // neighbouring ranges on different SMs
     c_begin = c_split * range;
     c_len = min(range, len - c_begin);                     // <= 0: no unit for this warp
+    if (c_nsplits > 1) {                                   // the same for every thread of the cluster
+      if (threadIdx.x == 0) {
+        const int owned = (a.group - static_cast<int>(c_rank) + static_cast<int>(c_size) - 1) / static_cast<int>(c_size);
+        mbar_init(smem_u32(&land_bar), 1);
+        mbar_fence_init();
+        // all of this block's heads' records, from every range; a block that owns no head (fewer heads
+        // than blocks) expects nothing and its barrier completes at once
+        mbar_arrive_expect_tx(smem_u32(&land_bar), static_cast<uint32_t>(owned * c_nsplits * kClusterRecord));
+      }
+      // publish the barriers: nobody sends before every block has armed its own (waited for below,
+      // right before the first send, by which time it has long completed)
+      __syncwarp();
+      asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    }
   }
   const int n_items = CLUSTER ? 0 : (TOK > 1 ? a.n_shared : (a.direct ? a.n_tokens : a.header->n_items));
   const int total = CLUSTER ? (c_len > 0 ? 1 : 0) : n_items * a.kv_heads;
@@ -498,49 +515,57 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   }
   if constexpr (CLUSTER) {
     if (c_nsplits > 1) {               // the same for every thread of the cluster
-      cluster_sync_all();              // every warp's partial is in its shared memory
-      const int CT = static_cast<int>(c_size) * WARPS * 32, ct = static_cast<int>(c_rank) * WARPS * 32 + threadIdx.x;
-      const int n4 = a.group * D / 4;  // groups of four neighbouring dims of the (token, kv head)'s output rows
-      for (int e4 = ct; e4 < n4; e4 += CT) {
-        const int h = (4 * e4) / D, d = 4 * e4 - h * D;
-        constexpr int B = 16;          // one round of loads for up to 16 ranges
-        float m_run = -INFINITY, l_run = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < c_nsplits; s0 += B) {
-          float2 ml[B];
-          float4 v[B];
-#pragma unroll
-          for (int i = 0; i < B; ++i) {
-            const int sp = s0 + i;
-            if (sp < c_nsplits) {
-              const uint32_t w_owner = static_cast<uint32_t>(sp) / c_size, r_owner = static_cast<uint32_t>(sp) - w_owner * c_size;
-              const uint32_t base = cluster_map(ring0 + w_owner * S::kWarpBytes, r_owner);
-              ml[i] = cluster_ld2(base + static_cast<uint32_t>(8 * NT * D + 2 * h) * 4u);
-              v[i] = cluster_ld4(base + static_cast<uint32_t>(h * D + d) * 4u);
-            } else {
-              ml[i] = make_float2(-INFINITY, 0.f);
-              v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // every block's landing barrier is armed
+      const uint32_t land0 = ring0 + WARPS * S::kWarpBytes;                   // landing area: behind the rings
+      const int ranges_max = WARPS * static_cast<int>(c_size);
+      if (c_len > 0) {
+        // send this warp's partial, head by head, to the heads' owners: 16 quads of sums and one with
+        // (maximum, sum) per head, read back from where the unit's finish left them
+        __syncwarp();
+        const float* pacc = reinterpret_cast<const float*>(ring_ptr);
+        const float* pml = pacc + 8 * NT * D;
+        for (int i = lane; i < a.group * 17; i += 32) {
+          const int h = i / 17, k = i - h * 17;
+          const uint32_t owner = static_cast<uint32_t>(h) % c_size, j = static_cast<uint32_t>(h) / c_size;
+          float4 v;
+          if (k < 16) {
+            v = *reinterpret_cast<const float4*>(pacc + h * D + 4 * k);
+          } else {
+            const float2 ml = *reinterpret_cast<const float2*>(pml + 2 * h);
+            v = make_float4(ml.x, ml.y, 0.f, 0.f);
           }
-          float mb = m_run;
-#pragma unroll
-          for (int i = 0; i < B; ++i) mb = fmaxf(mb, ml[i].x);
-          const float f0 = (m_run == -INFINITY) ? 0.f : exp2f(m_run - mb);
-          l_run *= f0;
-          acc.x *= f0; acc.y *= f0; acc.z *= f0; acc.w *= f0;
-#pragma unroll
-          for (int i = 0; i < B; ++i) {
-            const float f = (ml[i].x == -INFINITY) ? 0.f : exp2f(ml[i].x - mb);
-            l_run += f * ml[i].y;
-            acc.x += f * v[i].x; acc.y += f * v[i].y; acc.z += f * v[i].z; acc.w += f * v[i].w;
-          }
-          m_run = mb;
+          const uint32_t dst = land0 + (j * ranges_max + c_split) * kClusterRecord + 16 * k;
+          cluster_push4(cluster_map(dst, owner), v, cluster_map(smem_u32(&land_bar), owner));
+        }
+      }
+      // this block's heads: wait for all their records, fold them, write the rows
+      if (!mbar_wait(smem_u32(&land_bar), 0u)) {
+        if (threadIdx.x == 0) report_give_up(a, kErrConsumerWait);
+      }
+      const int owned = (a.group - static_cast<int>(c_rank) + static_cast<int>(c_size) - 1) / static_cast<int>(c_size);
+      const unsigned char* land_ptr = smem_raw + (land0 - smem_u32(smem_raw));
+      for (int e = threadIdx.x; e < owned * (D / 2); e += WARPS * 32) {     // one pair of dims per thread
+        const int j = e / (D / 2), d = 2 * (e - j * (D / 2));
+        const int h = j * static_cast<int>(c_size) + static_cast<int>(c_rank);
+        const unsigned char* rec0 = land_ptr + static_cast<size_t>(j) * ranges_max * kClusterRecord;
+        float m_run = -INFINITY;
+#pragma unroll 4
+        for (int sp = 0; sp < c_nsplits; ++sp) m_run = fmaxf(m_run, *reinterpret_cast<const float*>(rec0 + sp * kClusterRecord + 256));
+        float l_run = 0.f, acc0 = 0.f, acc1 = 0.f;
+#pragma unroll 4
+        for (int sp = 0; sp < c_nsplits; ++sp) {
+          const unsigned char* rec = rec0 + sp * kClusterRecord;
+          const float2 ml = *reinterpret_cast<const float2*>(rec + 256);
+          const float f = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - m_run);
+          const float2 v = *reinterpret_cast<const float2*>(rec + 4 * d);
+          l_run += f * ml.y;
+          acc0 += f * v.x;
+          acc1 += f * v.y;
         }
         const float inv = 1.f / l_run;
         T* o = out_row<T>(a, a.out, c_token) + static_cast<size_t>(c_kvh * a.group + h) * D + d;
-        *reinterpret_cast<uint2*>(o) = make_uint2(pack2<T>(acc.x * inv, acc.y * inv), pack2<T>(acc.z * inv, acc.w * inv));
+        *reinterpret_cast<uint32_t*>(o) = pack2<T>(acc0 * inv, acc1 * inv);
       }
-      cluster_sync_all();              // nobody leaves while its shared memory is still being read
     }
   }
 }

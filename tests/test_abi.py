@@ -107,9 +107,9 @@ def test_host_plan_layout_without_a_device(pkv):
     assert st == pkv._lib.PKV_E_ARG and b"negative" in L.pkv_last_error()
 
 
-def test_host_planner_offers_the_cluster_form_only_on_request(pkv, monkeypatch):
-    """pkv_decode_plan.cluster: set by the host planner only with PKV_DECODE_CLUSTER=1 in the environment
-    (read at every call), only for steps whose (token, kv head) pairs can each have a resident cluster
+def test_host_planner_offers_the_cluster_form_for_small_steps_only(pkv, monkeypatch):
+    """pkv_decode_plan.cluster: set by the host planner unless the environment has PKV_DECODE_CLUSTER=0
+    (read at every call), and only for steps whose (token, kv head) pairs can each have a resident cluster
     (3 blocks on each of the device's SMs; 148 assumed without a device) with at most 256 keys per warp,
     head_dim 64 and at most 8 query heads per kv head."""
     L = pkv.lib()
@@ -126,11 +126,12 @@ def test_host_planner_offers_the_cluster_form_only_on_request(pkv, monkeypatch):
         assert st == 0, L.pkv_last_error()
         return plan.cluster
 
-    monkeypatch.delenv("PKV_DECODE_CLUSTER", raising=False)
+    monkeypatch.setenv("PKV_DECODE_CLUSTER", "0")
     assert cluster_of([1000] * 8, 32, 4) == 0
-    monkeypatch.setenv("PKV_DECODE_CLUSTER", "1")
+    monkeypatch.delenv("PKV_DECODE_CLUSTER")
     assert cluster_of([1000] * 8, 32, 4) == 8            # 32 pairs: the largest portable cluster
     assert cluster_of([1000] * 64, 14, 2) == 3           # 128 pairs on 444 block slots
+    assert cluster_of([1000] * 40, 14, 2) == 4           # 80 pairs: 5 would fit; the kernel takes 2, 3, 4 or 8
     assert cluster_of([1000] * 111, 14, 2) == 2          # 222 pairs
     assert cluster_of([1000] * 112, 14, 2) == 0          # 224 pairs: two blocks each would not all be resident
     assert cluster_of([20000] * 8, 32, 4) == 0           # 626 keys per warp

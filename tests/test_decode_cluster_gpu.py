@@ -1,6 +1,7 @@
 """GPU parity for the small-step form of the decode attention: one thread-block cluster per (token,
 kv head), the history cut into one range per warp of the cluster, split-K merge inside the launch
-through the cluster's shared memory (decode_tma_kernel with CLUSTER).  The host planner chooses it
+(every warp sends its partial to the blocks that own the heads, through the cluster's shared memory;
+decode_tma_kernel with CLUSTER).  The host planner chooses it
 (pkv_decode_plan.cluster); results must match the CPU checker exactly as the ordinary form does."""
 import numpy as np
 import pytest
@@ -12,8 +13,9 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(autouse=True)
 def _cluster_form_on(monkeypatch):
-    """The cluster form is opt-in (PKV_DECODE_CLUSTER=1, read at every planning call)."""
-    monkeypatch.setenv("PKV_DECODE_CLUSTER", "1")
+    """The cluster form is the default for small steps; PKV_DECODE_CLUSTER=0 (read at every planning call)
+    switches it off, so make sure the environment does not."""
+    monkeypatch.delenv("PKV_DECODE_CLUSTER", raising=False)
 
 
 def _nb(ctx, bs):
@@ -28,13 +30,17 @@ def _nb(ctx, bs):
     (32, 4, 16, [64, 65, 127, 128, 129, 1023, 1024, 1025] * 4),        # 128 pairs: clusters of 3
     (8, 8, 32, [33, 200, 511]),                                        # one query head per kv head, block 32
     (16, 2, 16, [31, 32, 33, 63, 64, 95, 96, 97, 255, 256, 257]),      # range edges on slab boundaries
+    (14, 2, 16, [200 + 37 * i for i in range(40)]),                    # 80 pairs: 5 blocks would fit, clusters of 4
+    (14, 2, 16, [150 + 3 * i for i in range(100)]),                    # 200 pairs: clusters of 2
 ])
 def test_cluster_form_matches_checker(pkv, orc, torch_cuda, dtype, mode, shape):
     qh, kvh, bs, ctx = shape
     case = Case(orc, dtype, qh, kvh, 64, bs, _nb(ctx, bs), ctx, [1] * len(ctx), 77, pkv)
     want = case.expected(orc)
+    before = pkv.lib().pkv_debug_cluster_launches()
     d = case.run_gpu(pkv, torch_cuda, mode)
     assert d["plan"].plan.cluster >= 2, "the planner was expected to choose the cluster form for this step"
+    assert pkv.lib().pkv_debug_cluster_launches() == before + 1, "the launch fell back to the ordinary form"
     check_case(case, pkv, torch_cuda, orc, mode)
     del want
 
@@ -74,7 +80,7 @@ def test_planner_keeps_the_ordinary_form_for_large_or_long_steps(pkv, torch_cuda
     assert wide.plan.cluster == 0
     small = pkv.DecodePlan(8, 32, 4, 64).build_host(np.full(8, 1000, dtype=np.int32))
     assert small.plan.cluster == 8
-    monkeypatch.delenv("PKV_DECODE_CLUSTER")
+    monkeypatch.setenv("PKV_DECODE_CLUSTER", "0")
     off = pkv.DecodePlan(8, 32, 4, 64).build_host(np.full(8, 1000, dtype=np.int32))
     assert off.plan.cluster == 0
 
@@ -85,6 +91,8 @@ def test_configuration_2_at_full_size_through_clusters(pkv, orc, torch_cuda, wor
     w = workloads.make("cfg2", layers=1)
     ctx = [int(c) for c in w.ctx]
     case = Case(orc, "bf16", w.q_heads, w.kv_heads, w.head_dim, w.block_size, w.num_blocks, ctx, [1] * len(ctx), 1235, pkv)
+    before = pkv.lib().pkv_debug_cluster_launches()
     d = case.run_gpu(pkv, torch_cuda, "fused_append")
     assert d["plan"].plan.cluster == 3
+    assert pkv.lib().pkv_debug_cluster_launches() == before + 1, "the launch fell back to the ordinary form"
     check_case(case, pkv, torch_cuda, orc, "fused_append")
