@@ -210,6 +210,8 @@ typedef struct pkv_decode_plan {
                      warp -- unless the environment has PKV_DECODE_CLUSTER=0 (read at every call); the other
                      planners leave 0.  A caller may clear it; a launch the kernel or the device cannot take
                      (fp32 K/V, block_size < 16, clusters that would not all be resident) runs the ordinary form.
+                     A captured launch of this form stays correct when replayed over later steps of the same
+                     token count: it reads no plan, only token_pos.
                      No counterpart in llm-engine. */
   int pad[2];
 } pkv_decode_plan;
