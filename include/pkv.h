@@ -240,7 +240,17 @@ int pkv_decode_plan_host_image(const int* h_token_pos, int n_tokens, int q_heads
  * brings several needs its earlier new keys in the pool first: append, then
  * pkv_decode_attn_planned_*).  Runs where the TMA kernel runs (16-bit K/V, head_dim
  * 64 or 128, at most 16 query heads per kv head, block_size a power of two >= 16);
- * PKV_E_UNSUPPORTED otherwise, with nothing enqueued. */
+ * PKV_E_UNSUPPORTED otherwise, with nothing enqueued.
+ * Ordering: the launch is a programmatic dependent of the kernel before it on the stream and
+ * starts fetching the pools' rows of positions BELOW token_pos while that kernel is still
+ * running; q, k, v and slots are read, and everything is written, only after it has completed.
+ * So the rows of earlier positions must not be produced by the kernel directly before this call
+ * -- they never are in a decode step: they were written by earlier steps, and a step starts with
+ * uploads or planning that complete before anything behind them begins (and this library's
+ * block copy does not release its dependents early, so a copy-on-write copy directly before
+ * this call is safe).  A caller whose own kernel writes such rows directly before this call
+ * and releases its dependents early (griddepcontrol.launch_dependents) puts any other
+ * operation in between, or sets PKV_PDL=0. */
 int pkv_append_decode_attn_planned_f16(const pkv_decode_plan* plan, const void* q, const void* k, const void* v,
                                        const int* slots, void* k_cache, void* v_cache, const int* block_tables,
                                        const int* table_offset, const int* token_seq, const int* token_pos,

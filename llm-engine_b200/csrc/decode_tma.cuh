@@ -132,7 +132,9 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   // table offset, table entries -- run while the predecessor is still finishing.  What the predecessor
   // itself may have written (pool rows appended by the preceding launch, q and the new k / v rows, the
   // workspace the previous merge has finished with) is touched only after griddepcontrol.wait, which
-  // every lane executes in issue_next() right before the warp's first load is issued.
+  // every lane executes in issue_next() right before the warp's first load is issued -- or, with the
+  // append inside this launch, only before the unit's q rows are read (see there): the pool rows it
+  // loads are then all from earlier steps.
   pdl_launch_dependents();
   if (lane == 0) {
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(&kmap) : "memory");
@@ -223,9 +225,11 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
     int ent[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) ent[m] = __shfl_sync(0xffffffffu, i_ent, box0 + m - i_ent_base);
-    if (!waited) {
-      pdl_wait();
-      waited = true;
+    if constexpr (!FUSED_APPEND) {
+      if (!waited) {
+        pdl_wait();
+        waited = true;
+      }
     }
     // The slot's previous contents were read with ordinary loads (ldmatrix) by all
     // lanes; order those before the asynchronous-proxy write that refills it.
@@ -285,6 +289,17 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
 
     while (more && n_issued - n_consumed < NSTAGES) more = issue_next();
 
+    if constexpr (FUSED_APPEND) {
+      // With the append inside this launch the loads issued above fetch only rows of EARLIER steps (the
+      // newest row comes from the step's k / v below): they need not wait for the predecessor, which
+      // cannot be writing them -- a step's launches are preceded by that step's uploads or planning,
+      // which complete before anything behind them starts.  What the predecessor does produce -- q, the
+      // new k / v rows -- and everything this launch writes comes after this wait.
+      if (!waited) {
+        pdl_wait();
+        waited = true;
+      }
+    }
     // Q^T fragments (B operand): rows = dims, columns = heads of the group.
     uint32_t qb[KS][NT][2];
     {
@@ -515,6 +530,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_BLOCKS)
   }
   if constexpr (CLUSTER) {
     if (c_nsplits > 1) {               // the same for every thread of the cluster
+      if (!waited) pdl_wait();         // warps without a range write output rows too
       asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // every block's landing barrier is armed
       const uint32_t land0 = ring0 + WARPS * S::kWarpBytes;                   // landing area: behind the rings
       const int ranges_max = WARPS * static_cast<int>(c_size);

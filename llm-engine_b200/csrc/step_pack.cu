@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(kThreads, 1) step_pack_kernel(const StepPackAr
   __shared__ int s_status;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) s_status = 0;
-  pdl_launch_dependents();
+  // No early release of the dependents: the kernels behind this one read the arrays it writes before
+  // their own griddepcontrol.wait (they treat the step's index arrays as complete from the start).
   pdl_wait();
 
   // ---- 0. bring the resident tables up to date: releases first, then appended blocks ----
