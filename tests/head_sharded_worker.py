@@ -37,6 +37,10 @@ def main():
         idx = [i32(case.idx.block_tables), i32(case.idx.table_offset), i32(case.idx.token_seq), i32(case.idx.token_pos)]
         pkv.launch_store_kv(d["k"], d["v"], i32(case.idx.slots), d["kc"], d["vc"], case.N, kvl * hd)
         plan = pkv.DecodePlan(case.N, ql, kvl, hd, device=dev).build_host(case.idx.token_pos)
+        # The exchange lives in the merge kernel, so the peer call always takes the split-K form; ask the
+        # local call for the same (a step this small would otherwise run as thread-block clusters, which
+        # groups the keys differently and rounds differently).
+        plan.plan.cluster = 0
         # this rank's own columns are what the ordinary call computes for the same heads, bit for bit
         local = torch.zeros((case.N, ql * hd), dtype=d["q"].dtype, device=dev)
         plan.attention(d["q"], d["kc"], d["vc"], *idx, local, bs, case.scale)
