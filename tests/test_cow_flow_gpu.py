@@ -13,7 +13,10 @@ from tests.gpu_util import TOL, cast_like_reference, from_device, rel_errors, to
 pytestmark = pytest.mark.gpu
 
 
-def test_fork_cow_copy_append_decode(pkv, orc, torch_cuda):
+@pytest.mark.parametrize("fused", [False, True], ids=["append then attention", "append inside the attention launch"])
+def test_fork_cow_copy_append_decode(pkv, orc, torch_cuda, fused):
+    """fused: the attention launch then fetches the pools' older rows -- the copied blocks among them --
+    ahead of its dependency wait; the block copy before it does not release its dependents early."""
     torch = torch_cuda
     rng = np.random.default_rng(77)
     qh, kvh, hd, bs, nb, layers = 32, 4, 64, 16, 96, 3
@@ -68,10 +71,14 @@ def test_fork_cow_copy_append_decode(pkv, orc, torch_cuda):
             qb, qf = cast_like_reference(orc, rng.standard_normal((N, qh * hd), dtype=np.float32), "bf16")
             kb, kf = cast_like_reference(orc, rng.standard_normal((N, kv_dim), dtype=np.float32), "bf16")
             vb, vf = cast_like_reference(orc, rng.standard_normal((N, kv_dim), dtype=np.float32), "bf16")
-            pkv.launch_store_kv(to_device(torch, kb, "bf16"), to_device(torch, vb, "bf16"), i32(idx.slots),
-                                d_pool[2 * l], d_pool[2 * l + 1], N, kv_dim)
             out = torch.zeros((N, qh * hd), dtype=torch.bfloat16, device="cuda")
-            plan.attention(to_device(torch, qb, "bf16"), d_pool[2 * l], d_pool[2 * l + 1], *d_idx, out, bs, scale)
+            if fused:
+                plan.append_attention(to_device(torch, qb, "bf16"), to_device(torch, kb, "bf16"), to_device(torch, vb, "bf16"),
+                                      i32(idx.slots), d_pool[2 * l], d_pool[2 * l + 1], *d_idx, out, bs, scale)
+            else:
+                pkv.launch_store_kv(to_device(torch, kb, "bf16"), to_device(torch, vb, "bf16"), i32(idx.slots),
+                                    d_pool[2 * l], d_pool[2 * l + 1], N, kv_dim)
+                plan.attention(to_device(torch, qb, "bf16"), d_pool[2 * l], d_pool[2 * l + 1], *d_idx, out, bs, scale)
             orc.append(kb, vb, idx.slots, h_bits[2 * l], h_bits[2 * l + 1])
             orc.append(kf, vf, idx.slots, h_f32[2 * l], h_f32[2 * l + 1])
             want = orc.paged_attention(qf, h_f32[2 * l], h_f32[2 * l + 1], idx.block_tables, idx.table_offset,

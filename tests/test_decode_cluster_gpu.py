@@ -6,7 +6,7 @@ decode_tma_kernel with CLUSTER).  The host planner chooses it
 import numpy as np
 import pytest
 
-from tests.gpu_util import Case, check_case, from_device
+from tests.gpu_util import Case, check_case, from_device, rel_errors, to_device
 
 pytestmark = pytest.mark.gpu
 
@@ -96,3 +96,56 @@ def test_configuration_2_at_full_size_through_clusters(pkv, orc, torch_cuda, wor
     assert d["plan"].plan.cluster == 3
     assert pkv.lib().pkv_debug_cluster_launches() == before + 1, "the launch fell back to the ordinary form"
     check_case(case, pkv, torch_cuda, orc, "fused_append")
+
+
+def test_captured_cluster_launch_replays_over_later_steps(pkv, orc, torch_cuda):
+    """A cluster-form launch captured into a CUDA graph reads no plan, only the step's index arrays: replayed
+    over later steps of the same token count (every sequence a few keys longer, some across a block
+    boundary, the arrays rewritten in place) it must give those steps' results."""
+    torch = torch_cuda
+    qh, kvh, bs, nb = 14, 2, 16, 1024
+    base = [300, 705, 1100, 1513, 1900, 2040, 256, 999, 47, 1290]
+    cases = [Case(orc, "bf16", qh, kvh, 64, bs, nb, [c + 9 * s for c in base], [1] * len(base), 5, pkv) for s in range(3)]
+    N = cases[0].N
+    d = cases[0].upload(torch)
+    tab_len = max(c.idx.block_tables.size for c in cases)
+    d["block_tables"] = torch.zeros(tab_len, dtype=torch.int32, device="cuda")
+    plan = pkv.DecodePlan(N, qh, kvh, 64).build_host(cases[0].idx.token_pos)
+    assert plan.plan.cluster >= 2
+    args = lambda: (d["q"], d["k"], d["v"], d["slots"], d["kc"], d["vc"], d["block_tables"], d["table_offset"],
+                    d["token_seq"], d["token_pos"], d["out"], bs, cases[0].scale)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).cuda()
+
+    def load(case):
+        for name in ("kc", "vc", "q", "k", "v"):
+            d[name].copy_(to_device(torch, getattr(case, name + "_bits"), "bf16"))
+        d["block_tables"][:case.idx.block_tables.size].copy_(i32(case.idx.block_tables))
+        for name in ("slots", "token_seq", "token_pos", "table_offset"):
+            d[name].copy_(i32(getattr(case.idx, name)))
+        d["out"].zero_()
+
+    load(cases[0])
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        plan.append_attention(*args())                    # warm-up outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    before = pkv.lib().pkv_debug_cluster_launches()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        plan.append_attention(*args())
+    assert pkv.lib().pkv_debug_cluster_launches() == before + 1
+    for step, case in enumerate(cases):
+        load(case)
+        plan.build_host(case.idx.token_pos)               # what a serving loop does every step; the captured launch ignores it
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        want_kc, want_vc, want = case.expected(orc)
+        kcb, _ = from_device(torch, orc, d["kc"], "bf16")
+        assert np.array_equal(kcb, want_kc), f"step {step}: K pool differs from the reference append"
+        _, got = from_device(torch, orc, d["out"], "bf16")
+        e_ref, e_row = rel_errors(got.reshape(N * qh, 64), want.reshape(N * qh, 64))
+        assert e_row <= 2e-2, (step, e_ref, e_row)
+    assert pkv.debug_device_flags() == 0
