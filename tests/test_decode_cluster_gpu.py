@@ -149,3 +149,21 @@ def test_captured_cluster_launch_replays_over_later_steps(pkv, orc, torch_cuda):
         e_ref, e_row = rel_errors(got.reshape(N * qh, 64), want.reshape(N * qh, 64))
         assert e_row <= 2e-2, (step, e_ref, e_row)
     assert pkv.debug_device_flags() == 0
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_cluster_form_on_random_small_steps(pkv, orc, torch_cuda, seed):
+    """Seeded random small steps -- 1 to 110 sequences, 1 to 8 query heads per kv head, 1 to 8 kv heads,
+    block 16 or 32, histories of 1 to 3,000 keys, with and without the append inside the launch -- through
+    whichever form the planner picks (the cluster form for most), against the CPU checker."""
+    rng = np.random.default_rng(1000 + seed)
+    kvh = int(rng.choice([1, 2, 4, 8]))
+    group = int(rng.integers(1, 9))
+    bs = int(rng.choice([16, 32]))
+    n = int(rng.integers(1, max(2, 220 // kvh // 2)))
+    top = int(rng.choice([40, 300, 1200, 3000]))
+    ctx = [int(x) for x in rng.integers(0, top, size=n)]
+    dtype = "bf16" if seed % 2 == 0 else "f16"
+    mode = "fused_append" if seed % 3 else "host_plan"
+    case = Case(orc, dtype, group * kvh, kvh, 64, bs, _nb(ctx, bs), ctx, [1] * n, 4000 + seed, pkv)
+    check_case(case, pkv, torch_cuda, orc, mode)
