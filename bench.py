@@ -498,46 +498,65 @@ def run_ours(args, rank, local_rank, world):
     # its share out of its own pool, and the job's time is the slowest rank's.  One GPU: the deal is the
     # whole batch, i.e. the weak measurement itself.
     strong = None
+
+    def strong_share(world_v, rank_v):
+        """Rank rank_v's share of the batch dealt over world_v GPUs, timed on THIS GPU out of its own pools:
+        (ms per step, sequences, K/V bytes per layer, whether the append ran inside the attention launch)."""
+        sel = sh.deal_sequences(w.ctx, world_v, rank_v, "balanced")
+        tabs_s = [w.tables[i] for i in sel]
+        pos_s = np.asarray([int(w.ctx[i]) for i in sel], dtype=np.int32)
+        idx_s = pkv.pack_step(tabs_s, pos_s, bs)
+        Ns = idx_s.n_tokens
+        s_slots, s_seq, s_pos = i32(idx_s.slots), i32(idx_s.token_seq), i32(idx_s.token_pos)
+        s_tab, s_off = i32(idx_s.block_tables), i32(idx_s.table_offset)
+        plan_s = pkv.DecodePlan(Ns, w.q_heads, w.kv_heads, w.head_dim, device=dev)
+        fused_s = w.dtype != "f32" and (args.append == "fused" or (args.append == "auto" and Ns * w.kv_heads < 1024))
+        qs, ks, vs, os_ = [q[l][:Ns] for l in range(L)], [k[l][:Ns] for l in range(L)], [v[l][:Ns] for l in range(L)], [out[l][:Ns] for l in range(L)]
+
+        def step_strong():
+            plan_s.build_host(idx_s.token_pos)
+            for l in range(L):
+                if fused_s:
+                    plan_s.append_attention(qs[l], ks[l], vs[l], s_slots, kc_l[l], vc_l[l], s_tab, s_off, s_seq, s_pos, os_[l], bs, w.scale)
+                else:
+                    pkv.launch_store_kv(ks[l], vs[l], s_slots, kc_l[l], vc_l[l], Ns, kv_dim)
+                    plan_s.attention(qs[l], kc_l[l], vc_l[l], s_tab, s_off, s_seq, s_pos, os_[l], bs, w.scale)
+
+        step_strong()
+        torch.cuda.synchronize()
+        replay_s = step_strong
+        if not args.no_graph:
+            try:
+                gs = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gs):
+                    step_strong()
+                replay_s = gs.replay
+            except Exception as e:
+                sys.stderr.write(f"[bench] capture of the strong-scaling step failed, timing eager launches: {e}\n")
+                torch.cuda.synchronize()
+        ms = timed(replay_s, args.steps, args.warmup) / args.steps
+        L_all = (w.ctx + w.new).astype(np.int64)
+        my_bytes = float((2 * L_all[sel] * w.kv_heads * w.head_dim * w.elem_bytes).sum())
+        return ms, int(Ns), my_bytes, fused_s
+
     if not args.no_strong:
         if world == 1:
             strong = {"value": value, "unit": "tok/s", "ms_per_step": ms_step, "sequences_per_rank": [N],
                       "efficiency_vs_one_gpu": 1.0, "policy": "balanced (one rank: the whole batch)"}
+            if args.workload == "cfg3":
+                # What the deal over 2, 4 and 8 GPUs would give, from rank 0's share timed on this one GPU (the
+                # shares hold the same K/V bytes to 1e-5 and no collective is involved, so the slowest rank's time
+                # is this time up to run-to-run noise): the real multi-GPU figure is the `strong` block of a
+                # --gpus N run.
+                proj = {}
+                for wv in (2, 4, 8):
+                    ms_v, n_v, b_v, f_v = strong_share(wv, 0)
+                    proj[str(wv)] = {"sequences": n_v, "kv_bytes_per_layer": b_v, "ms_per_step": ms_v, "us_per_layer": ms_v * 1e3 / L,
+                                     "projected_tok_s": N / (ms_v * 1e-3), "projected_efficiency": (ms_step / wv) / ms_v,
+                                     "append": "inside the attention launch" if f_v else "separate launch"}
+                strong["one_gpu_share_of_a_deal_over"] = proj
         else:
-            sel = sh.deal_sequences(w.ctx, world, rank, "balanced")
-            tabs_s = [w.tables[i] for i in sel]
-            pos_s = np.asarray([int(w.ctx[i]) for i in sel], dtype=np.int32)
-            idx_s = pkv.pack_step(tabs_s, pos_s, bs)
-            Ns = idx_s.n_tokens
-            s_slots, s_seq, s_pos = i32(idx_s.slots), i32(idx_s.token_seq), i32(idx_s.token_pos)
-            s_tab, s_off = i32(idx_s.block_tables), i32(idx_s.table_offset)
-            plan_s = pkv.DecodePlan(Ns, w.q_heads, w.kv_heads, w.head_dim, device=dev)
-            fused_s = w.dtype != "f32" and (args.append == "fused" or (args.append == "auto" and Ns * w.kv_heads < 1024))
-            qs, ks, vs, os_ = [q[l][:Ns] for l in range(L)], [k[l][:Ns] for l in range(L)], [v[l][:Ns] for l in range(L)], [out[l][:Ns] for l in range(L)]
-
-            def step_strong():
-                plan_s.build_host(idx_s.token_pos)
-                for l in range(L):
-                    if fused_s:
-                        plan_s.append_attention(qs[l], ks[l], vs[l], s_slots, kc_l[l], vc_l[l], s_tab, s_off, s_seq, s_pos, os_[l], bs, w.scale)
-                    else:
-                        pkv.launch_store_kv(ks[l], vs[l], s_slots, kc_l[l], vc_l[l], Ns, kv_dim)
-                        plan_s.attention(qs[l], kc_l[l], vc_l[l], s_tab, s_off, s_seq, s_pos, os_[l], bs, w.scale)
-
-            step_strong()
-            torch.cuda.synchronize()
-            replay_s = step_strong
-            if not args.no_graph:
-                try:
-                    gs = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(gs):
-                        step_strong()
-                    replay_s = gs.replay
-                except Exception as e:
-                    sys.stderr.write(f"[bench] capture of the strong-scaling step failed, timing eager launches: {e}\n")
-                    torch.cuda.synchronize()
-            ms_s = timed(replay_s, args.steps, args.warmup) / args.steps
-            L_all = (w.ctx + w.new).astype(np.int64)
-            my_bytes = float((2 * L_all[sel] * w.kv_heads * w.head_dim * w.elem_bytes).sum())
+            ms_s, Ns, my_bytes, fused_s = strong_share(world, rank)
             gather = [None] * world
             dist.all_gather_object(gather, (int(Ns), my_bytes))
             strong = {"value": N / (ms_s * 1e-3), "unit": "tok/s", "ms_per_step": ms_s,
