@@ -65,8 +65,8 @@ const Tuning& tuning() {
 
 // PKV_DECODE_CLUSTER=0: the host planner never chooses the cluster form of the attention launch for small
 // steps (read at every planning call, so a process can switch it).  On by default: on the step it is
-// meant for (64 sequences, 256-2,048 keys) it is 8 % faster than the two ordinary launches inside a
-// replayed graph and 20 % faster launched eagerly.
+// meant for (64 sequences, 256-2,048 keys) a layer takes 10.3 us against 12.3 us for the two ordinary
+// launches inside a replayed graph, and a fifth less time launched eagerly.
 bool cluster_form_enabled() {
   const char* e = std::getenv("PKV_DECODE_CLUSTER");
   return !(e && e[0] == '0');
