@@ -45,6 +45,7 @@ WORKLOAD_TEXT = {
     "cfg3": "TinyLlama-1.1B decode step: 22 layers, 32q/4kv heads, d64, bf16 KV, 256 seqs, ctx log-uniform [128,8192], block 16, fragmented 65536-block pool per layer",
     "cfg4": "chunked prefill, Qwen2.5-0.5B attention shapes (14q/2kv heads, d64), bf16: 32 seqs, cached context U[0,1536] + 512-token chunk, causal over cached+new, block 16, shuffled tables; one step = append + prefill attention for 24 layers",
     "cfg5": "prefix-cache decode: TinyLlama shapes, 22 layers, 128 seqs sharing a 512-token prefix + suffix U[32,256], bf16 KV, block 16",
+    "mixed": "one attention call on a mixed step as llm-engine's forward pass packs it: two 300-token prefill chunks (1,200 and 700 cached tokens) + 20 decode tokens, Qwen2.5-0.5B shapes (14q/2kv heads, d64), f16, block 16",
     "cow": "copy-on-write block copy alone: TinyLlama shapes (4 kv heads, d64, bf16, block 16: 8 KiB blocks), 22 layers x 2 pools of 8192 blocks, 127 block pairs per wave on every pool in one launch, 8 disjoint pair lists in rotation",
 }
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the decode attention kernel, from the
@@ -1165,6 +1166,25 @@ def run_cow(args, rank, local_rank, world):
                           "cpu_baseline": None, "e2e": None, "gpu_launches": max(args.steps, 8) * 4, "clocks": clocks, "detail": res}), flush=True)
 
 
+def run_mixed(args, rank, local_rank, world):
+    """--workload mixed: the mixed step by itself (the router's kernels are easiest to profile this way)."""
+    import torch
+    pkv = importlib.import_module("llm-engine_b200")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    res = measure_mixed_step(pkv, torch, dev)
+    clocks = sampler.stop()
+    if rank == 0:
+        us = res["mixed_entry_point_us_per_call"]
+        print(json.dumps({"metric": "mixed-step attention calls per second (prefill chunks routed to the tensor-core kernel)", "value": 1e6 / us,
+                          "unit": "calls/s", "n_gpus": world, "steps": 30, "warmup": 5, "ms_per_step": us / 1e3,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": f"mixed: {WORKLOAD_TEXT['mixed']}"}, "roofline": None, "cpu_baseline": None, "e2e": None,
+                          "gpu_launches": None, "clocks": clocks, "detail": res}), flush=True)
+
+
 def secondary_measurements(args, pkv, wl, torch, dev, pools, w):
     """Short runs of the other kernels on the box the default line is measured on (one GPU only): the
     tcgen05 prefill kernel on configuration 4's launch, the small-batch decode step of configuration 2,
@@ -1274,6 +1294,8 @@ def main():
         run_prefix_cow(args, rank, local_rank, world)
     elif args.workload == "cow":
         run_cow(args, rank, local_rank, world)
+    elif args.workload == "mixed":
+        run_mixed(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 
